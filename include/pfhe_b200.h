@@ -1,0 +1,187 @@
+/*
+ * pfhe_b200 -- C ABI of the B200 (sm_100a) GGUF block-decode library.
+ *
+ * The reference project (phfe, src/phfe/inference/gguf_loader.py) is pure
+ * Python and has no FFI of its own; its boundary for this path is the Python
+ * API GGUFReader.read_tensor / StreamingDequantizer.iter_batches /
+ * GGUFModelPatcher.patch_context.  Every entry point below names the reference
+ * lines whose work it takes over.  All pointers are plain device or host
+ * addresses, all sizes are bytes or element counts, `stream` is a cudaStream_t
+ * passed as void* (NULL = the legacy default stream).
+ *
+ * Every function returns PFHE_OK (0) or a negative pfhe_status; nothing throws,
+ * nothing takes ownership of caller memory.  pfhe_last_error_string() returns a
+ * thread-local description of the most recent failure on the calling thread.
+ */
+#ifndef PFHE_B200_H
+#define PFHE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml tensor type ids, as in gguf_loader.py:33-47 (only the six the reference decodes). */
+enum pfhe_ggml_type {
+    PFHE_TYPE_F32 = 0,
+    PFHE_TYPE_F16 = 1,
+    PFHE_TYPE_Q4_0 = 2,
+    PFHE_TYPE_Q4_1 = 3,
+    PFHE_TYPE_Q8_0 = 8,
+    PFHE_TYPE_BF16 = 30
+};
+
+/* Output element types: the torch dtypes read_tensor(dtype=...) accepts on this path. */
+enum pfhe_out_dtype { PFHE_OUT_F32 = 0, PFHE_OUT_F16 = 1, PFHE_OUT_BF16 = 2 };
+
+enum pfhe_status {
+    PFHE_OK = 0,
+    PFHE_ERR_BAD_TYPE = -1,      /* ggml type outside the six above: NotImplementedError / ValueError in the reference (gguf_loader.py:134-135, :371-374) */
+    PFHE_ERR_BAD_DTYPE = -2,     /* output dtype not f32/f16/bf16 */
+    PFHE_ERR_SHORT_SOURCE = -3,  /* src_bytes < ceil(n/32)*block_bytes: ValueError "Data too short" (gguf_loader.py:444-446) */
+    PFHE_ERR_SHORT_DEST = -4,    /* dst_bytes < n_elements * sizeof(out) */
+    PFHE_ERR_BAD_ARG = -5,       /* NULL pointer, negative size, bad handle */
+    PFHE_ERR_CUDA = -6,          /* a CUDA runtime call failed; see pfhe_last_error_string() */
+    PFHE_ERR_TIMEOUT = -7,       /* a bounded wait ran out (host event wait or device barrier wait) */
+    PFHE_ERR_DEVICE_WAIT = -8    /* a decode kernel gave up waiting for its own bulk copy */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int pfhe_version(void);
+
+/* Thread-local text for the last non-zero status returned on this thread. */
+const char *pfhe_last_error_string(void);
+
+/*
+ * Packed size of n_elements of a ggml type: ceil(n/block_elems)*block_bytes.
+ * Replaces GGUFTensorInfo.nbytes (gguf_loader.py:131-139).  Returns
+ * PFHE_ERR_BAD_TYPE (negative) for an unsupported type.
+ */
+int64_t pfhe_tensor_nbytes(int ggml_type, int64_t n_elements);
+
+/*
+ * Decode one tensor (or one contiguous row slice) that is already resident in
+ * device memory.  Replaces the six decode functions plus the final cast of
+ * GGUFReader.read_tensor (gguf_loader.py:359-378, :407-554):
+ *   Q4_0: out[2j] = ((qs[j]&15)-8)*d, out[2j+1] = ((qs[j]>>4)-8)*d
+ *   Q4_1: out[2j] = (qs[j]&15)*d+m,   out[2j+1] = (qs[j]>>4)*d+m   (one fp32 rounding)
+ *   Q8_0: out[i]  = float(qs[i])*d
+ *   F16/BF16/F32: exact widening or copy
+ * then one round-to-nearest-even cast to out_dtype.  Results are bit-identical
+ * to the reference for all non-NaN values.
+ *
+ * src_dev may have any alignment and dst_dev any alignment that is a multiple of
+ * the output element size; 16-byte aligned destinations and 2-byte aligned
+ * sources take the fast kernels.  The launch is asynchronous on `stream`.
+ * Up to 15 bytes before src_dev and after src_dev+src_bytes, inside the
+ * enclosing 16-byte lines, may be read (never used).
+ */
+int pfhe_dequant_launch(int ggml_type, int out_dtype,
+                        const void *src_dev, int64_t src_bytes,
+                        void *dst_dev, int64_t dst_bytes,
+                        int64_t n_elements, void *stream);
+
+/*
+ * As pfhe_dequant_launch, but the decoded value is first rounded to mid_dtype
+ * and that result is converted to out_dtype.  Replaces
+ * read_tensor(dtype=mid) followed by param.copy_(tensor) into a parameter of
+ * another dtype in GGUFModelPatcher.patch_context (gguf_loader.py:746, :758-759).
+ * mid_dtype == out_dtype is the plain single rounding.
+ */
+int pfhe_dequant_launch_cast2(int ggml_type, int mid_dtype, int out_dtype,
+                              const void *src_dev, int64_t src_bytes,
+                              void *dst_dev, int64_t dst_bytes,
+                              int64_t n_elements, void *stream);
+
+/* Kernel selection and shape for experiments; zero fields mean "library default". */
+typedef struct pfhe_launch_cfg {
+    int32_t variant;      /* 0 default; 1 bulk-copy staged tiles; 2 direct global loads; 3 bulk-copy in and out; 9 per-element fallback */
+    int32_t tile_blocks;  /* quant blocks per shared-memory tile (multiple of 8) */
+    int32_t stages;       /* tiles in flight per CTA */
+    int32_t threads;      /* threads per CTA (multiple of 32) */
+    int32_t ctas_per_sm;  /* grid = SM count * ctas_per_sm */
+    int32_t streaming_stores; /* 1: evict-first stores; 0: default; -1: library default */
+    int32_t reserved[2];
+} pfhe_launch_cfg;
+
+int pfhe_dequant_launch_ex(int ggml_type, int mid_dtype, int out_dtype,
+                           const void *src_dev, int64_t src_bytes,
+                           void *dst_dev, int64_t dst_bytes,
+                           int64_t n_elements, void *stream,
+                           const pfhe_launch_cfg *cfg);
+
+/*
+ * Reads and clears the device-side wait status of `device` (-1 = current).
+ * A decode kernel that gave up waiting for one of its bulk copies records
+ * PFHE_ERR_DEVICE_WAIT here and returns without hanging.  Call after
+ * synchronising the stream.  Returns PFHE_OK if no kernel reported anything.
+ */
+int pfhe_device_status(int device);
+
+/* Number of kernels this library has launched in this process (all threads). */
+int64_t pfhe_launch_count(void);
+
+/* ------------------------------------------------------------------------- *
+ * Staged loader: host bytes -> pinned ring -> copy stream -> decode kernel.
+ * Takes over the host-to-device step of read_tensor (gguf_loader.py:356, :378):
+ * the reference decodes on the CPU and copies fp32 results from pageable memory
+ * synchronously; here the packed bytes are copied and decoded on the device,
+ * with the copy of chunk i+1 overlapping the decode of chunk i.
+ * ------------------------------------------------------------------------- */
+typedef struct pfhe_loader pfhe_loader;
+
+typedef struct pfhe_loader_stats {
+    int64_t bytes_staged;     /* packed bytes copied into pinned slots */
+    int64_t bytes_decoded;    /* output bytes produced */
+    int64_t chunks;           /* chunks submitted */
+    int64_t tensors;          /* pfhe_loader_submit calls */
+    double host_copy_seconds; /* wall time spent filling pinned slots */
+    double slot_wait_seconds; /* wall time spent waiting for a free slot */
+} pfhe_loader_stats;
+
+/*
+ * device: CUDA device ordinal.  n_slots pinned+device staging slots of
+ * slot_bytes each; a tensor larger than a slot is cut into chunks of whole
+ * 8-block groups, so every chunk starts on a 16-byte line on both sides.
+ * n_threads host threads fill the pinned slots (0 = pick from the host's core
+ * count).
+ */
+int pfhe_loader_create(int device, int n_slots, int64_t slot_bytes, int n_threads,
+                       pfhe_loader **out);
+
+/*
+ * Queue one tensor or row slice whose packed bytes are in ordinary host memory
+ * (for example an mmap of the GGUF file).  The call returns when every chunk
+ * has been copied into a pinned slot and its transfer and decode have been
+ * queued; the decode kernels run on `stream`, so work queued on `stream`
+ * afterwards sees the finished output.  host_src may be released as soon as the
+ * call returns.
+ */
+int pfhe_loader_submit(pfhe_loader *ld, const void *host_src, int64_t src_bytes,
+                       int ggml_type, int mid_dtype, int out_dtype,
+                       void *dst_dev, int64_t dst_bytes, int64_t n_elements,
+                       void *stream);
+
+/* As pfhe_loader_submit, reading the packed bytes with pread(fd, ..., file_offset). */
+int pfhe_loader_submit_fd(pfhe_loader *ld, int fd, int64_t file_offset, int64_t src_bytes,
+                          int ggml_type, int mid_dtype, int out_dtype,
+                          void *dst_dev, int64_t dst_bytes, int64_t n_elements,
+                          void *stream);
+
+/*
+ * Block until everything submitted so far has finished on the device, or until
+ * timeout_ms has passed (PFHE_ERR_TIMEOUT).  Also reports a device-side wait
+ * failure (PFHE_ERR_DEVICE_WAIT).
+ */
+int pfhe_loader_wait(pfhe_loader *ld, int timeout_ms);
+
+int pfhe_loader_get_stats(pfhe_loader *ld, pfhe_loader_stats *out);
+
+/* Waits (bounded) for outstanding work, then frees slots, streams and threads. */
+int pfhe_loader_destroy(pfhe_loader *ld);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PFHE_B200_H */

@@ -1,0 +1,103 @@
+"""ctypes binding of ``libpfhe_b200.so`` (declarations: ``include/pfhe_b200.h``).
+
+There is no fallback: if the library is missing or fails to load, importing
+callers get a ``RuntimeError`` that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libpfhe_b200.so")
+
+# enum pfhe_status
+OK = 0
+ERR_BAD_TYPE, ERR_BAD_DTYPE, ERR_SHORT_SOURCE, ERR_SHORT_DEST = -1, -2, -3, -4
+ERR_BAD_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_DEVICE_WAIT = -5, -6, -7, -8
+
+# enum pfhe_out_dtype
+OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
+
+# Every symbol include/pfhe_b200.h declares.
+EXPORTED_SYMBOLS = (
+    "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes",
+    "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex",
+    "pfhe_device_status", "pfhe_launch_count",
+    "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd",
+    "pfhe_loader_wait", "pfhe_loader_get_stats", "pfhe_loader_destroy",
+)
+
+
+class LaunchCfg(ctypes.Structure):
+    _fields_ = [("variant", ctypes.c_int32), ("tile_blocks", ctypes.c_int32), ("stages", ctypes.c_int32),
+                ("threads", ctypes.c_int32), ("ctas_per_sm", ctypes.c_int32), ("streaming_stores", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 2)]
+
+
+class LoaderStats(ctypes.Structure):
+    _fields_ = [("bytes_staged", ctypes.c_int64), ("bytes_decoded", ctypes.c_int64), ("chunks", ctypes.c_int64),
+                ("tensors", ctypes.c_int64), ("host_copy_seconds", ctypes.c_double),
+                ("slot_wait_seconds", ctypes.c_double)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the library once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA decode library has not been built. "
+            "Run `python -m pfhe_b200.build` (needs nvcc). There is no CPU fallback.")
+    L = ctypes.CDLL(LIB_PATH)
+    i32, i64, vp = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
+    L.pfhe_version.restype = i32
+    L.pfhe_last_error_string.restype = ctypes.c_char_p
+    L.pfhe_tensor_nbytes.restype = i64
+    L.pfhe_tensor_nbytes.argtypes = [i32, i64]
+    L.pfhe_dequant_launch.restype = i32
+    L.pfhe_dequant_launch.argtypes = [i32, i32, vp, i64, vp, i64, i64, vp]
+    L.pfhe_dequant_launch_cast2.restype = i32
+    L.pfhe_dequant_launch_cast2.argtypes = [i32, i32, i32, vp, i64, vp, i64, i64, vp]
+    L.pfhe_dequant_launch_ex.restype = i32
+    L.pfhe_dequant_launch_ex.argtypes = [i32, i32, i32, vp, i64, vp, i64, i64, vp, ctypes.POINTER(LaunchCfg)]
+    L.pfhe_device_status.restype = i32
+    L.pfhe_device_status.argtypes = [i32]
+    L.pfhe_launch_count.restype = i64
+    L.pfhe_loader_create.restype = i32
+    L.pfhe_loader_create.argtypes = [i32, i32, i64, i32, ctypes.POINTER(vp)]
+    L.pfhe_loader_submit.restype = i32
+    L.pfhe_loader_submit.argtypes = [vp, vp, i64, i32, i32, i32, vp, i64, i64, vp]
+    L.pfhe_loader_submit_fd.restype = i32
+    L.pfhe_loader_submit_fd.argtypes = [vp, i32, i64, i64, i32, i32, i32, vp, i64, i64, vp]
+    L.pfhe_loader_wait.restype = i32
+    L.pfhe_loader_wait.argtypes = [vp, i32]
+    L.pfhe_loader_get_stats.restype = i32
+    L.pfhe_loader_get_stats.argtypes = [vp, ctypes.POINTER(LoaderStats)]
+    L.pfhe_loader_destroy.restype = i32
+    L.pfhe_loader_destroy.argtypes = [vp]
+    _lib = L
+    return L
+
+
+def last_error() -> str:
+    msg = lib().pfhe_last_error_string()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(rc: int) -> None:
+    """Maps a pfhe_status to the exception type the reference raises for it."""
+    if rc == OK:
+        return
+    msg = last_error() or f"pfhe status {rc}"
+    if rc == ERR_BAD_TYPE:
+        raise NotImplementedError(msg)          # gguf_loader.py:371-374
+    if rc in (ERR_SHORT_SOURCE, ERR_SHORT_DEST, ERR_BAD_DTYPE, ERR_BAD_ARG):
+        raise ValueError(msg)                   # gguf_loader.py:444-446
+    if rc == ERR_TIMEOUT:
+        raise TimeoutError(msg)
+    raise RuntimeError(msg)

@@ -1,0 +1,357 @@
+// C ABI of the decode library: argument checks, kernel selection, launches.
+// The declarations and the reference lines each entry point replaces are in
+// include/pfhe_b200.h.  No arithmetic lives here.
+#include "common.h"
+#include "dequant_kernels.cuh"
+
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+
+namespace pfhe {
+
+thread_local std::string g_last_error;
+std::atomic<int64_t> g_launch_count{0};
+
+void set_error(const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+}
+
+int cuda_fail(cudaError_t e, const char *what)
+{
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return PFHE_ERR_CUDA;
+}
+
+// --- per-process device table ---------------------------------------------
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;
+int g_sm_count[kMaxDevices];
+bool g_sm_known[kMaxDevices];
+int *g_status_words = nullptr;                                  // pinned, mapped, one int per device
+std::unordered_map<const void *, uint64_t> g_smem_configured;   // kernel -> device bitmask
+}  // namespace
+
+int current_device(int *dev)
+{
+    cudaError_t e = cudaGetDevice(dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (*dev < 0 || *dev >= kMaxDevices) { set_error("device ordinal %d out of range", *dev); return PFHE_ERR_BAD_ARG; }
+    return PFHE_OK;
+}
+
+int sm_count(int dev, int *out)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_sm_known[dev]) {
+        int n = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        g_sm_count[dev] = n;
+        g_sm_known[dev] = true;
+    }
+    *out = g_sm_count[dev];
+    return PFHE_OK;
+}
+
+// The status words live in pinned host memory that every device can write:
+// a kernel only touches them when a bounded wait runs out, and the host can
+// read them without a copy.
+int status_word(int dev, int **out)
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_status_words) {
+        void *p = nullptr;
+        cudaError_t e = cudaHostAlloc(&p, kMaxDevices * sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaHostAlloc(status)");
+        memset(p, 0, kMaxDevices * sizeof(int));
+        g_status_words = static_cast<int *>(p);
+    }
+    *out = g_status_words + dev;
+    return PFHE_OK;
+}
+
+static int ensure_smem(const void *kernel, int dev, size_t bytes)
+{
+    if (bytes <= 48 * 1024) return PFHE_OK;
+    std::lock_guard<std::mutex> lk(g_mu);
+    uint64_t &mask = g_smem_configured[kernel];
+    if (mask & (1ull << dev)) return PFHE_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+    mask |= 1ull << dev;
+    return PFHE_OK;
+}
+
+// --- kernel tables ----------------------------------------------------------
+using StagedFn = void (*)(const BlockKernelArgs);
+using FlatFn = void (*)(const uint8_t *, void *, int64_t);
+
+struct BlockKernels {
+    StagedFn staged[2];      // [streaming stores]
+    StagedFn staged_out;
+    FlatFn direct[2];
+    FlatFn any;
+};
+struct ElemKernels {
+    FlatFn vec[2];
+    FlatFn any;
+};
+
+template <int T, int MID, int OUT> static BlockKernels block_kernels()
+{
+    return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
+                        dequant_blocks_staged_out<T, MID, OUT>,
+                        {dequant_blocks_direct<T, MID, OUT, false>, dequant_blocks_direct<T, MID, OUT, true>},
+                        dequant_any_alignment<T, MID, OUT>};
+}
+template <int T, int MID, int OUT> static ElemKernels elem_kernels()
+{
+    return ElemKernels{{convert_elements<T, MID, OUT, false>, convert_elements<T, MID, OUT, true>},
+                       dequant_any_alignment<T, MID, OUT>};
+}
+
+template <int T> static bool pick_block(int mid, int out, BlockKernels *k)
+{
+#define PFHE_CASE(M, O) if (mid == M && out == O) { *k = block_kernels<T, M, O>(); return true; }
+    PFHE_CASE(O_F32, O_F32) PFHE_CASE(O_F32, O_F16) PFHE_CASE(O_F32, O_BF16)
+    PFHE_CASE(O_F16, O_F32) PFHE_CASE(O_F16, O_F16) PFHE_CASE(O_F16, O_BF16)
+    PFHE_CASE(O_BF16, O_F32) PFHE_CASE(O_BF16, O_F16) PFHE_CASE(O_BF16, O_BF16)
+#undef PFHE_CASE
+    return false;
+}
+template <int T> static bool pick_elem(int mid, int out, ElemKernels *k)
+{
+#define PFHE_CASE(M, O) if (mid == M && out == O) { *k = elem_kernels<T, M, O>(); return true; }
+    PFHE_CASE(O_F32, O_F32) PFHE_CASE(O_F32, O_F16) PFHE_CASE(O_F32, O_BF16)
+    PFHE_CASE(O_F16, O_F32) PFHE_CASE(O_F16, O_F16) PFHE_CASE(O_F16, O_BF16)
+    PFHE_CASE(O_BF16, O_F32) PFHE_CASE(O_BF16, O_F16) PFHE_CASE(O_BF16, O_BF16)
+#undef PFHE_CASE
+    return false;
+}
+
+int type_geometry(int t, int *elems, int *bytes)
+{
+    switch (t) {
+    case T_F32: *elems = 1; *bytes = 4; return PFHE_OK;
+    case T_F16: case T_BF16: *elems = 1; *bytes = 2; return PFHE_OK;
+    case T_Q4_0: *elems = 32; *bytes = 18; return PFHE_OK;
+    case T_Q4_1: *elems = 32; *bytes = 20; return PFHE_OK;
+    case T_Q8_0: *elems = 32; *bytes = 34; return PFHE_OK;
+    default:
+        set_error("ggml type %d is not one of F32, F16, BF16, Q4_0, Q4_1, Q8_0", t);
+        return PFHE_ERR_BAD_TYPE;
+    }
+}
+
+int out_size(int o)
+{
+    switch (o) {
+    case O_F32: return 4;
+    case O_F16: case O_BF16: return 2;
+    default: return 0;
+    }
+}
+
+static int check_launch(cudaStream_t stream, const char *what)
+{
+    (void)stream;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return PFHE_OK;
+}
+
+// Default shapes, chosen from measurements on B200 (148 SMs).
+static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
+{
+    (void)out_dtype;
+    if (c->variant == 0) c->variant = 1;
+    if (c->threads <= 0) c->threads = 256;
+    if (c->stages <= 0) c->stages = 4;
+    if (c->ctas_per_sm <= 0) c->ctas_per_sm = 4;
+    if (c->tile_blocks <= 0) c->tile_blocks = (ggml_type == T_Q8_0) ? 256 : 512;
+    if (c->streaming_stores < 0) c->streaming_stores = 1;
+}
+
+int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_bytes, void *dst, int64_t dst_bytes,
+                  int64_t n, cudaStream_t stream, const pfhe_launch_cfg *user_cfg)
+{
+    int be = 0, bb = 0;
+    int rc = type_geometry(ggml_type, &be, &bb);
+    if (rc) return rc;
+    const int osz = out_size(out);
+    if (osz == 0 || out_size(mid) == 0) { set_error("output dtype %d / intermediate dtype %d not in {f32,f16,bf16}", out, mid); return PFHE_ERR_BAD_DTYPE; }
+    if (n < 0 || src_bytes < 0 || dst_bytes < 0) { set_error("negative size"); return PFHE_ERR_BAD_ARG; }
+    const int64_t need = (n + be - 1) / be * bb;
+    if (src_bytes < need) { set_error("Data too short: %lld < %lld", (long long)src_bytes, (long long)need); return PFHE_ERR_SHORT_SOURCE; }
+    if (dst_bytes < n * osz) { set_error("destination too small: %lld < %lld", (long long)dst_bytes, (long long)(n * osz)); return PFHE_ERR_SHORT_DEST; }
+    if (n == 0) return PFHE_OK;
+    if (!src || !dst) { set_error("null device pointer"); return PFHE_ERR_BAD_ARG; }
+    if (reinterpret_cast<uintptr_t>(dst) % osz) { set_error("destination not aligned to its element size"); return PFHE_ERR_BAD_ARG; }
+
+    int dev = 0, sms = 0;
+    if ((rc = current_device(&dev))) return rc;
+    if ((rc = sm_count(dev, &sms))) return rc;
+
+    pfhe_launch_cfg cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.streaming_stores = -1;
+    if (user_cfg) cfg = *user_cfg;
+    default_cfg(ggml_type, out, &cfg);
+    if (cfg.threads % 32 || cfg.threads > 512 || cfg.stages > kMaxStages || cfg.tile_blocks % 8) {
+        set_error("bad launch configuration"); return PFHE_ERR_BAD_ARG;
+    }
+    const int ss = cfg.streaming_stores ? 1 : 0;
+    const uintptr_t s = reinterpret_cast<uintptr_t>(src), d = reinterpret_cast<uintptr_t>(dst);
+    const uint8_t *src8 = static_cast<const uint8_t *>(src);
+    const int max_ctas = sms * cfg.ctas_per_sm;
+
+    if (be == 1) {                                                  // F32 / F16 / BF16 input
+        ElemKernels k;
+        bool ok = false;
+        if (ggml_type == T_F32) ok = pick_elem<T_F32>(mid, out, &k);
+        else if (ggml_type == T_F16) ok = pick_elem<T_F16>(mid, out, &k);
+        else ok = pick_elem<T_BF16>(mid, out, &k);
+        if (!ok) { set_error("no kernel"); return PFHE_ERR_BAD_DTYPE; }
+        const bool fast = cfg.variant != 9 && (s % 16 == 0) && (d % 16 == 0);
+        if (fast) {
+            const int wide = bb > osz ? bb : osz;
+            const int64_t steps = n / (16 / wide);
+            int64_t blocks = (steps + (int64_t)cfg.threads * 4 - 1) / ((int64_t)cfg.threads * 4);
+            if (blocks < 1) blocks = 1;
+            if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+            k.vec[ss]<<<(unsigned)blocks, cfg.threads, 0, stream>>>(src8, dst, n);
+        } else {
+            int64_t blocks = (n + 255) / 256;
+            if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
+            k.any<<<(unsigned)blocks, 256, 0, stream>>>(src8, dst, n);
+        }
+        return check_launch(stream, "element kernel launch");
+    }
+
+    BlockKernels k;
+    bool ok = false;
+    if (ggml_type == T_Q4_0) ok = pick_block<T_Q4_0>(mid, out, &k);
+    else if (ggml_type == T_Q4_1) ok = pick_block<T_Q4_1>(mid, out, &k);
+    else ok = pick_block<T_Q8_0>(mid, out, &k);
+    if (!ok) { set_error("no kernel"); return PFHE_ERR_BAD_DTYPE; }
+
+    const int64_t n_blocks = (n + 31) / 32;
+    int variant = cfg.variant;
+    if ((s % 2) || (d % 16)) variant = 9;                           // odd source or unaligned destination
+
+    if (variant == 9) {
+        int64_t blocks = (n + 255) / 256;
+        if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
+        k.any<<<(unsigned)blocks, 256, 0, stream>>>(src8, dst, n);
+        return check_launch(stream, "fallback kernel launch");
+    }
+    if (variant == 2) {
+        const int vec = 16 / osz;
+        const int64_t units = n / vec;
+        int64_t blocks = (units + (int64_t)cfg.threads * 4 - 1) / ((int64_t)cfg.threads * 4);
+        if (blocks < 1) blocks = 1;
+        if (blocks > max_ctas) blocks = max_ctas;
+        k.direct[ss]<<<(unsigned)blocks, cfg.threads, 0, stream>>>(src8, dst, n);
+        return check_launch(stream, "direct kernel launch");
+    }
+
+    BlockKernelArgs a;
+    a.skew = (int)(s & 15);
+    a.src16 = src8 - a.skew;
+    a.dst = dst;
+    a.n_elements = n;
+    a.n_blocks = n_blocks;
+    a.span_bytes = (a.skew + n_blocks * bb + 15) & ~(int64_t)15;
+    a.tile_blocks = cfg.tile_blocks;
+    a.stages = cfg.stages;
+    if ((rc = status_word(dev, &a.status))) return rc;
+
+    // Small tensors: fewer CTAs and shallower tiles, so every CTA has work.
+    const int64_t n_groups = (n_blocks + 7) / 8;
+    int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
+    const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
+    if (groups_per_cta * 8 < a.tile_blocks) a.tile_blocks = (int)(groups_per_cta * 8);
+    const int64_t tiles_per_cta = (groups_per_cta * 8 + a.tile_blocks - 1) / a.tile_blocks;
+    if (tiles_per_cta < a.stages) a.stages = (int)tiles_per_cta;
+
+    size_t smem = (size_t)a.stages * (a.tile_blocks * bb + 16);
+    StagedFn fn = k.staged[ss];
+    if (variant == 3) {
+        smem = ((smem + 127) & ~(size_t)127) + 2 * (size_t)a.tile_blocks * 32 * osz;
+        fn = k.staged_out;
+    }
+    if (smem > 227 * 1024) { set_error("tile configuration needs %zu bytes of shared memory", smem); return PFHE_ERR_BAD_ARG; }
+    if ((rc = ensure_smem(reinterpret_cast<const void *>(fn), dev, smem))) return rc;
+    fn<<<(unsigned)grid, cfg.threads, smem, stream>>>(a);
+    return check_launch(stream, "staged kernel launch");
+}
+
+}  // namespace pfhe
+
+using namespace pfhe;
+
+extern "C" {
+
+int pfhe_version(void) { return 100; }
+
+const char *pfhe_last_error_string(void) { return g_last_error.c_str(); }
+
+int64_t pfhe_tensor_nbytes(int ggml_type, int64_t n_elements)
+{
+    int be = 0, bb = 0;
+    int rc = type_geometry(ggml_type, &be, &bb);
+    if (rc) return rc;
+    if (n_elements < 0) { set_error("negative element count"); return PFHE_ERR_BAD_ARG; }
+    return (n_elements + be - 1) / be * bb;
+}
+
+int pfhe_dequant_launch(int ggml_type, int out_dtype, const void *src_dev, int64_t src_bytes, void *dst_dev,
+                        int64_t dst_bytes, int64_t n_elements, void *stream)
+{
+    return launch_decode(ggml_type, out_dtype, out_dtype, src_dev, src_bytes, dst_dev, dst_bytes, n_elements,
+                         static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int pfhe_dequant_launch_cast2(int ggml_type, int mid_dtype, int out_dtype, const void *src_dev, int64_t src_bytes,
+                              void *dst_dev, int64_t dst_bytes, int64_t n_elements, void *stream)
+{
+    return launch_decode(ggml_type, mid_dtype, out_dtype, src_dev, src_bytes, dst_dev, dst_bytes, n_elements,
+                         static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int pfhe_dequant_launch_ex(int ggml_type, int mid_dtype, int out_dtype, const void *src_dev, int64_t src_bytes,
+                           void *dst_dev, int64_t dst_bytes, int64_t n_elements, void *stream,
+                           const pfhe_launch_cfg *cfg)
+{
+    return launch_decode(ggml_type, mid_dtype, out_dtype, src_dev, src_bytes, dst_dev, dst_bytes, n_elements,
+                         static_cast<cudaStream_t>(stream), cfg);
+}
+
+int pfhe_device_status(int device)
+{
+    int dev = device;
+    int rc;
+    if (dev < 0 && (rc = current_device(&dev))) return rc;
+    if (dev >= 64) { set_error("device ordinal %d out of range", dev); return PFHE_ERR_BAD_ARG; }
+    int *w = nullptr;
+    if ((rc = status_word(dev, &w))) return rc;
+    const int v = __atomic_exchange_n(w, 0, __ATOMIC_SEQ_CST);
+    if (v == DEV_WAIT_TIMEOUT) {
+        set_error("a decode kernel on device %d gave up waiting for its bulk copy", dev);
+        return PFHE_ERR_DEVICE_WAIT;
+    }
+    return PFHE_OK;
+}
+
+int64_t pfhe_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,26 @@
+// Shared host-side declarations of the decode library (not part of the ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+
+#include "../../include/pfhe_b200.h"
+
+namespace pfhe {
+
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+int current_device(int *dev);
+int type_geometry(int ggml_type, int *block_elems, int *block_bytes);
+int out_size(int out_dtype);
+
+// Validates and launches one decode on `stream` (current device).
+int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_bytes, void *dst, int64_t dst_bytes,
+                  int64_t n_elements, cudaStream_t stream, const pfhe_launch_cfg *cfg);
+
+}  // namespace pfhe

@@ -1,0 +1,669 @@
+// Hand-written sm_100a kernels for GGUF block decode (Q4_0, Q4_1, Q8_0, F16,
+// BF16, F32 -> fp32 / fp16 / bf16).  The arithmetic follows the reference's
+// src/phfe/inference/gguf_loader.py:407-554 and the cast at :377-378 and is
+// bit-identical to it for every non-NaN value:
+//   Q4_0  out[2j] = float((qs[j]&15)-8)*d ; out[2j+1] = float((qs[j]>>4)-8)*d
+//   Q4_1  out[2j] = fma(qs[j]&15, d, m)   ; out[2j+1] = fma(qs[j]>>4, d, m)
+//   Q8_0  out[i]  = float(int8 qs[i])*d
+// followed by one round-to-nearest-even conversion (two when MID != OUT).
+//
+// The work is HBM-bound byte shuffling; there are no tensor-core operations.
+// Quantised blocks are 18/20/34 bytes, so only every 8th block starts on a
+// 16-byte line.  The main kernel therefore stages whole 8-block groups into
+// shared memory with cp.async.bulk (1-D TMA, no multicast, completion on an
+// mbarrier), unpacks from shared memory with 2-byte aligned reads, and writes
+// fully coalesced 16-byte stores.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pfhe {
+
+enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q8_0 = 8, T_BF16 = 30 };
+enum : int { O_F32 = 0, O_F16 = 1, O_BF16 = 2 };
+
+// Device-side status codes written to the status word.
+enum : int { DEV_OK = 0, DEV_WAIT_TIMEOUT = 1 };
+
+template <int T> struct Fmt;
+template <> struct Fmt<T_F32>  { static constexpr int kElems = 1,  kBytes = 4;  };
+template <> struct Fmt<T_F16>  { static constexpr int kElems = 1,  kBytes = 2;  };
+template <> struct Fmt<T_BF16> { static constexpr int kElems = 1,  kBytes = 2;  };
+template <> struct Fmt<T_Q4_0> { static constexpr int kElems = 32, kBytes = 18; };
+template <> struct Fmt<T_Q4_1> { static constexpr int kElems = 32, kBytes = 20; };
+template <> struct Fmt<T_Q8_0> { static constexpr int kElems = 32, kBytes = 34; };
+
+template <int O> struct OutT;
+template <> struct OutT<O_F32>  { using type = float;    static constexpr int kSize = 4; };
+template <> struct OutT<O_F16>  { using type = uint16_t; static constexpr int kSize = 2; };
+template <> struct OutT<O_BF16> { using type = uint16_t; static constexpr int kSize = 2; };
+
+// ---------------------------------------------------------------------------
+// Scalar conversions (all round-to-nearest-even, subnormals kept: this file
+// must be compiled without -use_fast_math / -ftz=true).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float half_bits_to_f32(uint32_t h)
+{
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
+{
+    __half2 h = __floats2half2_rn(lo, hi);          // cvt.rn.f16x2.f32
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);  // cvt.rn.bf16x2.f32
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// Round v to MID and widen back (identity for fp32).
+template <int MID> __device__ __forceinline__ float round_via(float v)
+{
+    if constexpr (MID == O_F16) return __half2float(__float2half_rn(v));
+    else if constexpr (MID == O_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    else return v;
+}
+
+template <int MID, int OUT> __device__ __forceinline__ uint32_t pack2(float a, float b)
+{
+    if constexpr (MID != OUT) { a = round_via<MID>(a); b = round_via<MID>(b); }
+    if constexpr (OUT == O_F16) return pack_f16x2(a, b);
+    else return pack_bf16x2(a, b);
+}
+
+template <int MID, int OUT> __device__ __forceinline__ void store_scalar(void *dst, int64_t i, float v)
+{
+    if constexpr (MID != OUT) v = round_via<MID>(v);
+    if constexpr (OUT == O_F32) reinterpret_cast<float *>(dst)[i] = v;
+    else if constexpr (OUT == O_F16) reinterpret_cast<__half *>(dst)[i] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16 *>(dst)[i] = __float2bfloat16_rn(v);
+}
+
+// ---------------------------------------------------------------------------
+// 2-byte reads.  kShared: the pointer is into the shared-memory tile (plain
+// generic load, lowered to LDS after inlining); otherwise a read-only global
+// load.
+// ---------------------------------------------------------------------------
+template <bool kShared> __device__ __forceinline__ uint32_t ld16(const uint8_t *p)
+{
+    if constexpr (kShared) return *reinterpret_cast<const uint16_t *>(p);
+    else return __ldg(reinterpret_cast<const unsigned short *>(p));
+}
+
+// ---------------------------------------------------------------------------
+// Exact small-integer -> float tricks.
+//   as_float(0x4B000000 | u) = 2^23 + u          (u < 2^23, ulp 1)
+//   as_float(0x49000000 | (n << 4)) = 2^19 + n   (n < 16, ulp 1/16)
+//   as_half(0x6400 | u) = 1024 + u               (u < 1024, ulp 1)
+//   as_half(0x5400 | (n << 4)) = 64 + n          (n < 16, ulp 1/16)
+// ---------------------------------------------------------------------------
+
+// Nibble j (0..3 = byte index) of w: low / high nibble as float minus `bias`.
+template <int J> __device__ __forceinline__ float nib_lo_f32(uint32_t w, float bias)
+{
+    uint32_t t = __byte_perm(w, 0x4B000000u, 0x7540 + J) & 0xFFFFFF0Fu;
+    return __fsub_rn(__uint_as_float(t), 8388608.0f + bias);
+}
+template <int J> __device__ __forceinline__ float nib_hi_f32(uint32_t w, float bias)
+{
+    uint32_t t = __byte_perm(w, 0x49000000u, 0x7540 + J) & 0xFFFFFFF0u;
+    return __fsub_rn(__uint_as_float(t), 524288.0f + bias);
+}
+// Byte j of u (already xor 0x80 biased int8) as float.
+template <int J> __device__ __forceinline__ float s8_f32(uint32_t u)
+{
+    uint32_t t = __byte_perm(u, 0x4B000000u, 0x7540 + J);
+    return __fsub_rn(__uint_as_float(t), 8388736.0f);
+}
+
+__device__ __forceinline__ uint32_t h2_sub_mul(uint32_t x, uint32_t c, uint32_t d2)
+{
+    __half2 hx = *reinterpret_cast<__half2 *>(&x);
+    __half2 hc = *reinterpret_cast<__half2 *>(&c);
+    __half2 hd = *reinterpret_cast<__half2 *>(&d2);
+    __half2 r = __hmul2_rn(__hsub2_rn(hx, hc), hd);   // exact subtract, one rounding in the multiply
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+// ---------------------------------------------------------------------------
+// Sixteen output bytes ("unit") of a quantised tensor.
+// VEC = 8 outputs for 16-bit targets, 4 for fp32.  `blk` points at the start of
+// the 18/20/34-byte block, `c` is the unit's index inside the block.
+// ---------------------------------------------------------------------------
+template <int T, int MID, int OUT, bool kShared>
+__device__ __forceinline__ uint4 decode_unit(const uint8_t *blk, int c)
+{
+    uint4 r;
+    if constexpr (T == T_Q4_0 || T == T_Q4_1) {
+        constexpr int kQs = (T == T_Q4_0) ? 2 : 4;
+        const uint32_t dbits = ld16<kShared>(blk);
+        if constexpr (OUT == O_F32) {
+            // 4 outputs from 2 packed bytes
+            const uint32_t w = ld16<kShared>(blk + kQs + 2 * c);
+            const float d = half_bits_to_f32(dbits);
+            float v0, v1, v2, v3;
+            if constexpr (T == T_Q4_0) {
+                v0 = __fmul_rn(nib_lo_f32<0>(w, 8.0f), d);
+                v1 = __fmul_rn(nib_hi_f32<0>(w, 8.0f), d);
+                v2 = __fmul_rn(nib_lo_f32<1>(w, 8.0f), d);
+                v3 = __fmul_rn(nib_hi_f32<1>(w, 8.0f), d);
+            } else {
+                const float m = half_bits_to_f32(ld16<kShared>(blk + 2));
+                v0 = __fmaf_rn(nib_lo_f32<0>(w, 0.0f), d, m);
+                v1 = __fmaf_rn(nib_hi_f32<0>(w, 0.0f), d, m);
+                v2 = __fmaf_rn(nib_lo_f32<1>(w, 0.0f), d, m);
+                v3 = __fmaf_rn(nib_hi_f32<1>(w, 0.0f), d, m);
+            }
+            r.x = __float_as_uint(round_via<MID>(v0));
+            r.y = __float_as_uint(round_via<MID>(v1));
+            r.z = __float_as_uint(round_via<MID>(v2));
+            r.w = __float_as_uint(round_via<MID>(v3));
+        } else {
+            // 8 outputs from 4 packed bytes
+            const uint32_t w = ld16<kShared>(blk + kQs + 4 * c) | (ld16<kShared>(blk + kQs + 4 * c + 2) << 16);
+            if constexpr (T == T_Q4_0 && MID == O_F16 && OUT == O_F16) {
+                // (q-8)*d has at most 15 significant bits, so the fp32 product the
+                // reference rounds to fp16 is exact and a single fp16 multiply of the
+                // exactly-represented (q-8) by d gives the same bits.
+                const uint32_t d2 = dbits * 0x10001u;
+                const uint32_t bias = 0x54806408u;   // half2(1032, 72): (1024+lo)-1032, (64+hi)-72
+                r.x = h2_sub_mul((__byte_perm(w, 0, 0x4040) & 0x00F0000Fu) | 0x54006400u, bias, d2);
+                r.y = h2_sub_mul((__byte_perm(w, 0, 0x4141) & 0x00F0000Fu) | 0x54006400u, bias, d2);
+                r.z = h2_sub_mul((__byte_perm(w, 0, 0x4242) & 0x00F0000Fu) | 0x54006400u, bias, d2);
+                r.w = h2_sub_mul((__byte_perm(w, 0, 0x4343) & 0x00F0000Fu) | 0x54006400u, bias, d2);
+            } else {
+                const float d = half_bits_to_f32(dbits);
+                float v[8];
+                if constexpr (T == T_Q4_0) {
+                    v[0] = __fmul_rn(nib_lo_f32<0>(w, 8.0f), d); v[1] = __fmul_rn(nib_hi_f32<0>(w, 8.0f), d);
+                    v[2] = __fmul_rn(nib_lo_f32<1>(w, 8.0f), d); v[3] = __fmul_rn(nib_hi_f32<1>(w, 8.0f), d);
+                    v[4] = __fmul_rn(nib_lo_f32<2>(w, 8.0f), d); v[5] = __fmul_rn(nib_hi_f32<2>(w, 8.0f), d);
+                    v[6] = __fmul_rn(nib_lo_f32<3>(w, 8.0f), d); v[7] = __fmul_rn(nib_hi_f32<3>(w, 8.0f), d);
+                } else {
+                    const float m = half_bits_to_f32(ld16<kShared>(blk + 2));
+                    v[0] = __fmaf_rn(nib_lo_f32<0>(w, 0.0f), d, m); v[1] = __fmaf_rn(nib_hi_f32<0>(w, 0.0f), d, m);
+                    v[2] = __fmaf_rn(nib_lo_f32<1>(w, 0.0f), d, m); v[3] = __fmaf_rn(nib_hi_f32<1>(w, 0.0f), d, m);
+                    v[4] = __fmaf_rn(nib_lo_f32<2>(w, 0.0f), d, m); v[5] = __fmaf_rn(nib_hi_f32<2>(w, 0.0f), d, m);
+                    v[6] = __fmaf_rn(nib_lo_f32<3>(w, 0.0f), d, m); v[7] = __fmaf_rn(nib_hi_f32<3>(w, 0.0f), d, m);
+                }
+                r.x = pack2<MID, OUT>(v[0], v[1]);
+                r.y = pack2<MID, OUT>(v[2], v[3]);
+                r.z = pack2<MID, OUT>(v[4], v[5]);
+                r.w = pack2<MID, OUT>(v[6], v[7]);
+            }
+        }
+    } else {  // T_Q8_0
+        const uint32_t dbits = ld16<kShared>(blk);
+        if constexpr (OUT == O_F32) {
+            const uint8_t *q = blk + 2 + 4 * c;
+            const uint32_t u = (ld16<kShared>(q) | (ld16<kShared>(q + 2) << 16)) ^ 0x80808080u;
+            const float d = half_bits_to_f32(dbits);
+            r.x = __float_as_uint(round_via<MID>(__fmul_rn(s8_f32<0>(u), d)));
+            r.y = __float_as_uint(round_via<MID>(__fmul_rn(s8_f32<1>(u), d)));
+            r.z = __float_as_uint(round_via<MID>(__fmul_rn(s8_f32<2>(u), d)));
+            r.w = __float_as_uint(round_via<MID>(__fmul_rn(s8_f32<3>(u), d)));
+        } else {
+            const uint8_t *q = blk + 2 + 8 * c;
+            const uint32_t u0 = (ld16<kShared>(q) | (ld16<kShared>(q + 2) << 16)) ^ 0x80808080u;
+            const uint32_t u1 = (ld16<kShared>(q + 4) | (ld16<kShared>(q + 6) << 16)) ^ 0x80808080u;
+            if constexpr (MID == O_F16 && OUT == O_F16) {
+                // q*d has at most 19 significant bits: exact in fp32, so one fp16
+                // multiply of the exactly-represented q by d rounds identically.
+                const uint32_t d2 = dbits * 0x10001u;
+                const uint32_t bias = 0x64806480u;   // half2(1152, 1152): (1024 + q + 128) - 1152
+                r.x = h2_sub_mul(__byte_perm(u0, 0x64646464u, 0x4140), bias, d2);
+                r.y = h2_sub_mul(__byte_perm(u0, 0x64646464u, 0x4342), bias, d2);
+                r.z = h2_sub_mul(__byte_perm(u1, 0x64646464u, 0x4140), bias, d2);
+                r.w = h2_sub_mul(__byte_perm(u1, 0x64646464u, 0x4342), bias, d2);
+            } else {
+                const float d = half_bits_to_f32(dbits);
+                r.x = pack2<MID, OUT>(__fmul_rn(s8_f32<0>(u0), d), __fmul_rn(s8_f32<1>(u0), d));
+                r.y = pack2<MID, OUT>(__fmul_rn(s8_f32<2>(u0), d), __fmul_rn(s8_f32<3>(u0), d));
+                r.z = pack2<MID, OUT>(__fmul_rn(s8_f32<0>(u1), d), __fmul_rn(s8_f32<1>(u1), d));
+                r.w = pack2<MID, OUT>(__fmul_rn(s8_f32<2>(u1), d), __fmul_rn(s8_f32<3>(u1), d));
+            }
+        }
+    }
+    return r;
+}
+
+// One decoded element of any format in fp32, byte-wise reads (any alignment).
+template <int T> __device__ __forceinline__ float decode_element_bytes(const uint8_t *src, int64_t i)
+{
+    if constexpr (T == T_F32) {
+        const uint8_t *p = src + 4 * i;
+        return __uint_as_float((uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24));
+    } else if constexpr (T == T_F16) {
+        const uint8_t *p = src + 2 * i;
+        return half_bits_to_f32((uint32_t)p[0] | ((uint32_t)p[1] << 8));
+    } else if constexpr (T == T_BF16) {
+        const uint8_t *p = src + 2 * i;
+        return bf16_bits_to_f32((uint32_t)p[0] | ((uint32_t)p[1] << 8));
+    } else {
+        const uint8_t *b = src + (i >> 5) * Fmt<T>::kBytes;
+        const int k = (int)(i & 31);
+        const float d = half_bits_to_f32((uint32_t)b[0] | ((uint32_t)b[1] << 8));
+        if constexpr (T == T_Q8_0) {
+            return __fmul_rn((float)(int)(int8_t)b[2 + k], d);
+        } else if constexpr (T == T_Q4_0) {
+            const uint32_t byte = b[2 + (k >> 1)];
+            const int q = (int)((k & 1) ? (byte >> 4) : (byte & 15)) - 8;
+            return __fmul_rn((float)q, d);
+        } else {
+            const float m = half_bits_to_f32((uint32_t)b[2] | ((uint32_t)b[3] << 8));
+            const uint32_t byte = b[4 + (k >> 1)];
+            const int q = (int)((k & 1) ? (byte >> 4) : (byte & 15));
+            return __fmaf_rn((float)q, d, m);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier / bulk-copy primitives (inline PTX, sm_90+; used here on sm_100a).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when the barrier did not complete within limit_ns.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint64_t limit_ns)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t spins = 0; spins < 0x40000000u; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 63u && global_timer_ns() - t0 > limit_ns) return false;
+    }
+    return false;
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// Both addresses 16-byte aligned, `bytes` a multiple of 16.  No multicast.
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// 1-D bulk copy shared -> global (bulk async-group completion).
+__device__ __forceinline__ void bulk_s2g(void *gdst, const void *smem_src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+template <bool kStream> __device__ __forceinline__ void store16(void *p, uint4 v)
+{
+    if constexpr (kStream) __stcs(reinterpret_cast<uint4 *>(p), v);
+    else *reinterpret_cast<uint4 *>(p) = v;
+}
+
+constexpr uint64_t kDeviceWaitLimitNs = 2000000000ull;   // 2 s: far beyond any healthy copy
+constexpr int kMaxStages = 8;
+
+struct BlockKernelArgs {
+    const uint8_t *src16;   // source rounded down to a 16-byte line
+    int32_t skew;           // src - src16 (even, 0..14)
+    void *dst;              // 16-byte aligned
+    int64_t n_elements;
+    int64_t n_blocks;       // ceil(n_elements / 32)
+    int64_t span_bytes;     // bytes from src16 to the 16-byte-rounded end of the packed data
+    int32_t tile_blocks;    // multiple of 8
+    int32_t stages;         // 1..kMaxStages
+    int *status;            // device-visible status word (pinned host memory)
+};
+
+// ---------------------------------------------------------------------------
+// Variant 1: bulk-copy staged tiles in, coalesced 16-byte stores out.
+// Each CTA owns one contiguous run of 8-block groups and walks it in tiles of
+// `tile_blocks` blocks through a `stages`-deep ring of shared-memory buffers.
+// ---------------------------------------------------------------------------
+template <int T, int MID, int OUT, bool kStream>
+__global__ void __launch_bounds__(512) dequant_blocks_staged(const BlockKernelArgs a)
+{
+    constexpr int BB = Fmt<T>::kBytes;
+    constexpr int VEC = 16 / OutT<OUT>::kSize;       // outputs per 16-byte store
+    constexpr int UPB = 32 / VEC;                    // units per block
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full[kMaxStages];
+
+    const int stage_bytes = a.tile_blocks * BB + 16;
+    const int64_t n_groups = (a.n_blocks + 7) >> 3;
+    const int64_t g0 = n_groups * blockIdx.x / gridDim.x;
+    const int64_t g1 = n_groups * (blockIdx.x + 1) / gridDim.x;
+    const int64_t b0 = g0 << 3;
+    const int64_t b1 = (g1 << 3) < a.n_blocks ? (g1 << 3) : a.n_blocks;
+    if (b1 <= b0) return;
+    const int n_tiles = (int)((b1 - b0 + a.tile_blocks - 1) / a.tile_blocks);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    auto issue = [&](int t) {
+        const int s = t % a.stages;
+        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
+        const int64_t nb = (b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks;
+        const int64_t off = tb0 * BB;                              // multiple of 16
+        int64_t bytes = (nb * BB + a.skew + 15) & ~(int64_t)15;
+        if (off + bytes > a.span_bytes) bytes = a.span_bytes - off;
+        mbar_expect_tx(&full[s], (uint32_t)bytes);
+        bulk_g2s(smem + (size_t)s * stage_bytes, a.src16 + off, (uint32_t)bytes, &full[s]);
+    };
+
+    if (threadIdx.x == 0) {
+        const int pre = n_tiles < a.stages ? n_tiles : a.stages;
+        for (int t = 0; t < pre; ++t) issue(t);
+    }
+
+    int waited_ok = 1;
+    int t = 0;
+    for (; t < n_tiles; ++t) {
+        const int s = t % a.stages;
+        const uint32_t parity = (uint32_t)(t / a.stages) & 1u;
+        if (!mbar_wait_bounded(&full[s], parity, kDeviceWaitLimitNs)) waited_ok = 0;
+        // Every thread must agree before touching the tile or leaving the loop.
+        if (__syncthreads_or(!waited_ok)) break;
+
+        const uint8_t *tile = smem + (size_t)s * stage_bytes + a.skew;
+        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
+        const int nb = (int)((b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks);
+        const int64_t e0 = tb0 << 5;
+        int64_t rem = a.n_elements - e0;                           // > 0
+        const int tile_elems = nb << 5;
+        const int valid = rem < tile_elems ? (int)rem : tile_elems;
+        const int full_units = valid / VEC;
+        uint8_t *out = reinterpret_cast<uint8_t *>(a.dst) + e0 * OutT<OUT>::kSize;
+
+#pragma unroll 4
+        for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
+            const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
+            store16<kStream>(out + (size_t)u * 16, r);
+        }
+        // Ragged end of the tensor (n_elements not a multiple of VEC): scalar stores.
+        if (valid % VEC != 0 && threadIdx.x == 0) {
+            for (int e = full_units * VEC; e < valid; ++e)
+                store_scalar<MID, OUT>(a.dst, e0 + e, decode_element_bytes<T>(tile, e));
+        }
+        __syncthreads();                                           // all reads of stage s done
+        if (threadIdx.x == 0 && t + a.stages < n_tiles) issue(t + a.stages);
+    }
+
+    if (t < n_tiles) {
+        // A wait ran out.  Report it, then give copies already issued a bounded
+        // chance to land before the shared memory is released.
+        if (threadIdx.x == 0) {
+            atomicExch(a.status, DEV_WAIT_TIMEOUT);
+            const int last = (t + a.stages) < n_tiles ? (t + a.stages) : n_tiles;
+            for (int k = t; k < last; ++k)
+                (void)mbar_wait_bounded(&full[k % a.stages], (uint32_t)(k / a.stages) & 1u, kDeviceWaitLimitNs / 8);
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Variant 3: bulk copies in AND out.  Results are written to a shared-memory
+// output tile with 16-byte STS and leave through cp.async.bulk shared->global,
+// so the LSU only ever touches shared memory.  Only whole tiles that lie fully
+// inside n_elements take the bulk store; a ragged last tile uses direct stores.
+// ---------------------------------------------------------------------------
+template <int T, int MID, int OUT>
+__global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKernelArgs a)
+{
+    constexpr int BB = Fmt<T>::kBytes;
+    constexpr int VEC = 16 / OutT<OUT>::kSize;
+    constexpr int UPB = 32 / VEC;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full[kMaxStages];
+
+    const int stage_bytes = a.tile_blocks * BB + 16;
+    const int out_tile_bytes = a.tile_blocks * 32 * OutT<OUT>::kSize;
+    uint8_t *out_smem = smem + (((size_t)a.stages * stage_bytes + 127) & ~(size_t)127);   // two buffers
+    const int64_t n_groups = (a.n_blocks + 7) >> 3;
+    const int64_t g0 = n_groups * blockIdx.x / gridDim.x;
+    const int64_t g1 = n_groups * (blockIdx.x + 1) / gridDim.x;
+    const int64_t b0 = g0 << 3;
+    const int64_t b1 = (g1 << 3) < a.n_blocks ? (g1 << 3) : a.n_blocks;
+    if (b1 <= b0) return;
+    const int n_tiles = (int)((b1 - b0 + a.tile_blocks - 1) / a.tile_blocks);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    auto issue = [&](int t) {
+        const int s = t % a.stages;
+        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
+        const int64_t nb = (b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks;
+        const int64_t off = tb0 * BB;
+        int64_t bytes = (nb * BB + a.skew + 15) & ~(int64_t)15;
+        if (off + bytes > a.span_bytes) bytes = a.span_bytes - off;
+        mbar_expect_tx(&full[s], (uint32_t)bytes);
+        bulk_g2s(smem + (size_t)s * stage_bytes, a.src16 + off, (uint32_t)bytes, &full[s]);
+    };
+
+    if (threadIdx.x == 0) {
+        const int pre = n_tiles < a.stages ? n_tiles : a.stages;
+        for (int t = 0; t < pre; ++t) issue(t);
+    }
+
+    int waited_ok = 1;
+    int t = 0;
+    for (; t < n_tiles; ++t) {
+        const int s = t % a.stages;
+        const uint32_t parity = (uint32_t)(t / a.stages) & 1u;
+        if (!mbar_wait_bounded(&full[s], parity, kDeviceWaitLimitNs)) waited_ok = 0;
+        // The output buffer used two tiles ago must have been read out by its bulk store.
+        if (threadIdx.x == 0) bulk_wait_read<1>();
+        if (__syncthreads_or(!waited_ok)) break;
+
+        const uint8_t *tile = smem + (size_t)s * stage_bytes + a.skew;
+        uint8_t *obuf = out_smem + (size_t)(t & 1) * out_tile_bytes;
+        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
+        const int nb = (int)((b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks);
+        const int64_t e0 = tb0 << 5;
+        const int64_t rem = a.n_elements - e0;
+        const int tile_elems = nb << 5;
+        const int valid = rem < tile_elems ? (int)rem : tile_elems;
+        const int full_units = valid / VEC;
+        uint8_t *gout = reinterpret_cast<uint8_t *>(a.dst) + e0 * OutT<OUT>::kSize;
+        const bool bulk_ok = (valid == tile_elems);               // whole blocks only: byte count is a multiple of 64
+
+        if (bulk_ok) {
+#pragma unroll 4
+            for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
+                const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
+                *reinterpret_cast<uint4 *>(obuf + (size_t)u * 16) = r;
+            }
+            fence_proxy_async_smem();                              // make the STS visible to the async proxy
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                bulk_s2g(gout, obuf, (uint32_t)(valid * OutT<OUT>::kSize));
+                bulk_commit();
+                if (t + a.stages < n_tiles) issue(t + a.stages);
+            }
+        } else {
+            for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
+                const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
+                store16<false>(gout + (size_t)u * 16, r);
+            }
+            if (valid % VEC != 0 && threadIdx.x == 0) {
+                for (int e = full_units * VEC; e < valid; ++e)
+                    store_scalar<MID, OUT>(a.dst, e0 + e, decode_element_bytes<T>(tile, e));
+            }
+            __syncthreads();
+            if (threadIdx.x == 0 && t + a.stages < n_tiles) issue(t + a.stages);
+        }
+    }
+    if (threadIdx.x == 0) bulk_wait_all<0>();                      // stores complete before smem is released
+
+    if (t < n_tiles) {
+        if (threadIdx.x == 0) {
+            atomicExch(a.status, DEV_WAIT_TIMEOUT);
+            const int last = (t + a.stages) < n_tiles ? (t + a.stages) : n_tiles;
+            for (int k = t; k < last; ++k)
+                (void)mbar_wait_bounded(&full[k % a.stages], (uint32_t)(k / a.stages) & 1u, kDeviceWaitLimitNs / 8);
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Variant 2: no shared memory; each thread reads its 2-byte pieces straight
+// from global memory (they hit in L1: a warp touches 144..272 contiguous bytes).
+// Source must be 2-byte aligned, destination 16-byte aligned.
+// ---------------------------------------------------------------------------
+template <int T, int MID, int OUT, bool kStream>
+__global__ void __launch_bounds__(512) dequant_blocks_direct(const uint8_t *__restrict__ src, void *__restrict__ dst,
+                                                             int64_t n_elements)
+{
+    constexpr int BB = Fmt<T>::kBytes;
+    constexpr int VEC = 16 / OutT<OUT>::kSize;
+    constexpr int UPB = 32 / VEC;
+    const int64_t full_units = n_elements / VEC;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    uint8_t *out = reinterpret_cast<uint8_t *>(dst);
+#pragma unroll 4
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < full_units; u += stride) {
+        const uint4 r = decode_unit<T, MID, OUT, false>(src + (u / UPB) * BB, (int)(u % UPB));
+        store16<kStream>(out + u * 16, r);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        for (int64_t e = full_units * VEC; e < n_elements; ++e)
+            store_scalar<MID, OUT>(dst, e, decode_element_bytes<T>(src, e));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Element-wise formats (F32 / F16 / BF16 in).  Each thread moves 16 bytes of the
+// wider side with one vector access.  Both pointers 16-byte aligned.
+// ---------------------------------------------------------------------------
+template <int T> __device__ __forceinline__ float widen16(uint32_t bits)
+{
+    if constexpr (T == T_F16) return half_bits_to_f32(bits & 0xFFFFu);
+    else return bf16_bits_to_f32(bits & 0xFFFFu);
+}
+
+template <int T, int MID, int OUT>
+__device__ __forceinline__ uint32_t convert_pair16(uint32_t two)   // two 16-bit inputs -> two 16-bit outputs
+{
+    if constexpr ((T == T_F16 && MID == O_F16 && OUT == O_F16) || (T == T_BF16 && MID == O_BF16 && OUT == O_BF16))
+        return two;                                                // passthrough is bit-exact, NaN payloads included
+    else
+        return pack2<MID, OUT>(widen16<T>(two), widen16<T>(two >> 16));
+}
+
+template <int T, int MID, int OUT, bool kStream>
+__global__ void __launch_bounds__(512) convert_elements(const uint8_t *__restrict__ src, void *__restrict__ dst,
+                                                        int64_t n_elements)
+{
+    constexpr int IN_SZ = Fmt<T>::kBytes;
+    constexpr int OUT_SZ = OutT<OUT>::kSize;
+    constexpr int WIDE = IN_SZ > OUT_SZ ? IN_SZ : OUT_SZ;
+    constexpr int EPT = 16 / WIDE;                                 // elements per thread step: 8 (2->2) or 4
+    const int64_t n_steps = n_elements / EPT;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    uint8_t *out = reinterpret_cast<uint8_t *>(dst);
+#pragma unroll 4
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_steps; i += stride) {
+        if constexpr (IN_SZ == 2 && OUT_SZ == 2) {
+            uint4 v = __ldcs(reinterpret_cast<const uint4 *>(src) + i);
+            v.x = convert_pair16<T, MID, OUT>(v.x); v.y = convert_pair16<T, MID, OUT>(v.y);
+            v.z = convert_pair16<T, MID, OUT>(v.z); v.w = convert_pair16<T, MID, OUT>(v.w);
+            store16<kStream>(out + i * 16, v);
+        } else if constexpr (IN_SZ == 2 && OUT_SZ == 4) {
+            const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(src) + i);
+            uint4 r;
+            r.x = __float_as_uint(round_via<MID>(widen16<T>(v.x)));
+            r.y = __float_as_uint(round_via<MID>(widen16<T>(v.x >> 16)));
+            r.z = __float_as_uint(round_via<MID>(widen16<T>(v.y)));
+            r.w = __float_as_uint(round_via<MID>(widen16<T>(v.y >> 16)));
+            store16<kStream>(out + i * 16, r);
+        } else if constexpr (IN_SZ == 4 && OUT_SZ == 2) {
+            const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(src) + i);
+            uint2 r;
+            r.x = pack2<MID, OUT>(__uint_as_float(v.x), __uint_as_float(v.y));
+            r.y = pack2<MID, OUT>(__uint_as_float(v.z), __uint_as_float(v.w));
+            if constexpr (kStream) __stcs(reinterpret_cast<uint2 *>(out) + i, r);
+            else reinterpret_cast<uint2 *>(out)[i] = r;
+        } else {                                                   // F32 -> F32 (possibly via a 16-bit rounding)
+            uint4 v = __ldcs(reinterpret_cast<const uint4 *>(src) + i);
+            if constexpr (MID != O_F32) {
+                v.x = __float_as_uint(round_via<MID>(__uint_as_float(v.x)));
+                v.y = __float_as_uint(round_via<MID>(__uint_as_float(v.y)));
+                v.z = __float_as_uint(round_via<MID>(__uint_as_float(v.z)));
+                v.w = __float_as_uint(round_via<MID>(__uint_as_float(v.w)));
+            }
+            store16<kStream>(out + i * 16, v);
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        for (int64_t e = n_steps * EPT; e < n_elements; ++e)
+            store_scalar<MID, OUT>(dst, e, decode_element_bytes<T>(src, e));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Variant 9: one thread per element, byte reads; any alignment, any size.
+// ---------------------------------------------------------------------------
+template <int T, int MID, int OUT>
+__global__ void __launch_bounds__(256) dequant_any_alignment(const uint8_t *__restrict__ src, void *__restrict__ dst,
+                                                             int64_t n_elements)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elements; i += stride) {
+        if constexpr ((T == T_F16 && MID == O_F16 && OUT == O_F16) || (T == T_BF16 && MID == O_BF16 && OUT == O_BF16)) {
+            const uint8_t *p = src + 2 * i;                        // bit-exact passthrough
+            reinterpret_cast<uint16_t *>(dst)[i] = (uint16_t)(p[0] | (p[1] << 8));
+        } else {
+            store_scalar<MID, OUT>(dst, i, decode_element_bytes<T>(src, i));
+        }
+    }
+}
+
+}  // namespace pfhe

@@ -1,0 +1,620 @@
+"""GGUF tensor loader with B200 decode -- drop-in for ``phfe.inference.gguf_loader``.
+
+Same names, signatures, defaults, return values and exceptions as the
+reference module (src/phfe/inference/gguf_loader.py).  The header and
+tensor-info parser stays in Python; the per-block decode
+(reference :407-554) and the cast (:377-378) run as sm_100a CUDA kernels
+reached through the C ABI in ``include/pfhe_b200.h``.  Packed bytes travel
+mmap -> pinned ring -> copy stream -> decode kernel; the dequantised tensor is
+never materialised on the host.
+
+Additions are keyword-only and default to the reference's behaviour:
+``read_tensor(..., rows=(start, stop), out=tensor)`` and
+``patch_context(..., shard=(rank, world_size), replicate_group=None)``.
+
+There is no CPU decode here.  ``device="cpu"`` results are decoded on the
+current CUDA device and copied back, so they carry the same bits; without a
+CUDA device every decode call raises ``RuntimeError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import fnmatch
+import logging
+import mmap
+import struct
+from contextlib import contextmanager
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, Iterator, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _native
+
+logger = logging.getLogger(__name__)
+
+# ---------------------------------------------------------------------------
+# Constants (reference :29-98)
+# ---------------------------------------------------------------------------
+GGUF_MAGIC = 0x46554747
+GGUF_VERSION = 3
+
+GGML_TYPE_F32 = 0
+GGML_TYPE_F16 = 1
+GGML_TYPE_Q4_0 = 2
+GGML_TYPE_Q4_1 = 3
+GGML_TYPE_Q5_0 = 6
+GGML_TYPE_Q5_1 = 7
+GGML_TYPE_Q8_0 = 8
+GGML_TYPE_Q8_1 = 9
+GGML_TYPE_Q2_K = 10
+GGML_TYPE_Q3_K = 11
+GGML_TYPE_Q4_K = 12
+GGML_TYPE_Q5_K = 13
+GGML_TYPE_Q6_K = 14
+GGML_TYPE_Q8_K = 15
+GGML_TYPE_BF16 = 30
+
+QK4_0 = QK4_1 = QK5_0 = QK5_1 = QK8_0 = QK8_1 = 32
+
+# ggml type -> (elements per block, bytes per block); the kernels' contract.
+QUANT_INFO = {
+    GGML_TYPE_F32: (1, 4),
+    GGML_TYPE_F16: (1, 2),
+    GGML_TYPE_BF16: (1, 2),
+    GGML_TYPE_Q4_0: (32, 18),
+    GGML_TYPE_Q4_1: (32, 20),
+    GGML_TYPE_Q8_0: (32, 34),
+}
+
+GGUF_TYPE_NAMES = {
+    GGML_TYPE_F32: "F32", GGML_TYPE_F16: "F16", GGML_TYPE_BF16: "BF16",
+    GGML_TYPE_Q4_0: "Q4_0", GGML_TYPE_Q4_1: "Q4_1", GGML_TYPE_Q5_0: "Q5_0", GGML_TYPE_Q5_1: "Q5_1",
+    GGML_TYPE_Q8_0: "Q8_0", GGML_TYPE_Q8_1: "Q8_1", GGML_TYPE_Q2_K: "Q2_K", GGML_TYPE_Q3_K: "Q3_K",
+    GGML_TYPE_Q4_K: "Q4_K", GGML_TYPE_Q5_K: "Q5_K", GGML_TYPE_Q6_K: "Q6_K", GGML_TYPE_Q8_K: "Q8_K",
+}
+
+(GGUF_METADATA_VALUE_TYPE_UINT8, GGUF_METADATA_VALUE_TYPE_INT8, GGUF_METADATA_VALUE_TYPE_UINT16,
+ GGUF_METADATA_VALUE_TYPE_INT16, GGUF_METADATA_VALUE_TYPE_UINT32, GGUF_METADATA_VALUE_TYPE_INT32,
+ GGUF_METADATA_VALUE_TYPE_FLOAT32, GGUF_METADATA_VALUE_TYPE_BOOL, GGUF_METADATA_VALUE_TYPE_STRING,
+ GGUF_METADATA_VALUE_TYPE_ARRAY, GGUF_METADATA_VALUE_TYPE_UINT64, GGUF_METADATA_VALUE_TYPE_INT64,
+ GGUF_METADATA_VALUE_TYPE_FLOAT64) = range(13)
+
+# scalar metadata types -> (struct code, numpy dtype)
+_SCALARS = {
+    GGUF_METADATA_VALUE_TYPE_UINT8: ("<B", "<u1"), GGUF_METADATA_VALUE_TYPE_INT8: ("<b", "<i1"),
+    GGUF_METADATA_VALUE_TYPE_UINT16: ("<H", "<u2"), GGUF_METADATA_VALUE_TYPE_INT16: ("<h", "<i2"),
+    GGUF_METADATA_VALUE_TYPE_UINT32: ("<I", "<u4"), GGUF_METADATA_VALUE_TYPE_INT32: ("<i", "<i4"),
+    GGUF_METADATA_VALUE_TYPE_UINT64: ("<Q", "<u8"), GGUF_METADATA_VALUE_TYPE_INT64: ("<q", "<i8"),
+    GGUF_METADATA_VALUE_TYPE_FLOAT32: ("<f", "<f4"), GGUF_METADATA_VALUE_TYPE_FLOAT64: ("<d", "<f8"),
+}
+
+_TORCH_TO_OUT = {torch.float32: _native.OUT_F32, torch.float16: _native.OUT_F16, torch.bfloat16: _native.OUT_BF16}
+
+
+# ---------------------------------------------------------------------------
+# Data structures (reference :105-151)
+# ---------------------------------------------------------------------------
+@dataclass
+class GGUFTensorInfo:
+    """Metadata of one tensor: name, ggml dims (fastest axis first), type, offset."""
+    name: str
+    n_dims: int
+    dims: Tuple[int, ...]
+    dtype: int
+    offset: int
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for d in self.dims:
+            n *= d
+        return n
+
+    @property
+    def shape(self) -> Tuple[int, ...]:
+        """Row-major torch shape: the ggml dims reversed (reference :122-125)."""
+        return tuple(reversed(self.dims))
+
+    @property
+    def dtype_name(self) -> str:
+        return GGUF_TYPE_NAMES.get(self.dtype, f"UNKNOWN({self.dtype})")
+
+    @property
+    def nbytes(self) -> int:
+        """ceil(numel / block elements) * block bytes (reference :131-139)."""
+        if self.dtype not in QUANT_INFO:
+            raise ValueError(f"Unknown dtype {self.dtype} for size calculation")
+        per_block, block_bytes = QUANT_INFO[self.dtype]
+        return -(-self.numel // per_block) * block_bytes
+
+
+@dataclass
+class GGUFHeader:
+    magic: int
+    version: int
+    n_tensors: int
+    n_kv: int
+    metadata: Dict[str, Any] = field(default_factory=dict)
+    tensors: Dict[str, GGUFTensorInfo] = field(default_factory=dict)
+    tensor_data_offset: int = 0
+
+
+# ---------------------------------------------------------------------------
+# Device-side plumbing shared by every reader on a device
+# ---------------------------------------------------------------------------
+class _Stager:
+    """Owns one native staged loader (pinned ring + copy stream) per CUDA device."""
+
+    _by_device: Dict[int, "_Stager"] = {}
+    slot_bytes = 64 << 20
+    n_slots = 4
+    n_threads = 0
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        handle = ctypes.c_void_p()
+        _native.check(_native.lib().pfhe_loader_create(device_index, self.n_slots, self.slot_bytes,
+                                                       self.n_threads, ctypes.byref(handle)))
+        self.handle = handle
+
+    @classmethod
+    def get(cls, device_index: int) -> "_Stager":
+        st = cls._by_device.get(device_index)
+        if st is None:
+            st = cls._by_device[device_index] = cls(device_index)
+        return st
+
+    @classmethod
+    def shutdown(cls) -> None:
+        for st in cls._by_device.values():
+            _native.lib().pfhe_loader_destroy(st.handle)
+        cls._by_device.clear()
+
+    def submit(self, host_addr: int, nbytes: int, ggml_type: int, mid: int, out: int, dst: torch.Tensor,
+               numel: int) -> None:
+        stream = torch.cuda.current_stream(dst.device).cuda_stream
+        _native.check(_native.lib().pfhe_loader_submit(
+            self.handle, host_addr, nbytes, ggml_type, mid, out,
+            dst.data_ptr(), dst.numel() * dst.element_size(), numel, stream))
+
+    def wait(self, timeout_ms: int = 600000) -> None:
+        _native.check(_native.lib().pfhe_loader_wait(self.handle, timeout_ms))
+
+    def stats(self) -> Dict[str, float]:
+        s = _native.LoaderStats()
+        _native.check(_native.lib().pfhe_loader_get_stats(self.handle, ctypes.byref(s)))
+        return {name: getattr(s, name) for name, _ in s._fields_}
+
+
+def _cuda_device_for(device) -> Tuple[torch.device, torch.device]:
+    """(device the caller asked for, CUDA device that decodes)."""
+    want = torch.device(device)
+    if not torch.cuda.is_available():
+        raise RuntimeError("pfhe_b200 decodes GGUF tensors on a CUDA device (B200, sm_100a); "
+                           "no CUDA device is available and there is no CPU fallback")
+    if want.type == "cuda":
+        index = want.index if want.index is not None else torch.cuda.current_device()
+        want = torch.device("cuda", index)
+        return want, want
+    return want, torch.device("cuda", torch.cuda.current_device())
+
+
+# ---------------------------------------------------------------------------
+# Parser (reference :158-323)
+# ---------------------------------------------------------------------------
+class GGUFReader:
+    """Memory-mapped GGUF reader; use as a context manager.
+
+        with GGUFReader("model.gguf") as reader:
+            w = reader.read_tensor("blk.0.attn_q.weight", device="cuda", dtype=torch.float16)
+    """
+
+    def __init__(self, path: str | Path):
+        self.path = Path(path)
+        self._file = None
+        self._mmap = None
+        self._view: Optional[np.ndarray] = None      # uint8 view of the mmap (for host addresses)
+        self._header: Optional[GGUFHeader] = None
+        self._cursor = 0
+
+    def __enter__(self) -> "GGUFReader":
+        self._file = open(self.path, "rb")
+        try:
+            self._mmap = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_READ)
+            self._parse_header()
+        except BaseException:
+            self.__exit__(None, None, None)
+            raise
+        return self
+
+    def __exit__(self, *exc):
+        self._view = None
+        if self._mmap is not None:
+            try:
+                self._mmap.close()
+            except BufferError:        # a caller still holds a view; the map dies with it
+                pass
+            self._mmap = None
+        if self._file is not None:
+            self._file.close()
+            self._file = None
+
+    @property
+    def header(self) -> GGUFHeader:
+        if self._header is None:
+            raise RuntimeError("File not opened - use context manager")
+        return self._header
+
+    @property
+    def metadata(self) -> Dict[str, Any]:
+        return self.header.metadata
+
+    @property
+    def tensors(self) -> Dict[str, GGUFTensorInfo]:
+        return self.header.tensors
+
+    # -- little-endian cursor reads -----------------------------------------
+    def _take(self, code: str, size: int):
+        (v,) = struct.unpack_from(code, self._mmap, self._cursor)
+        self._cursor += size
+        return v
+
+    def _read_u32(self) -> int:
+        return self._take("<I", 4)
+
+    def _read_u64(self) -> int:
+        return self._take("<Q", 8)
+
+    def _read_string(self) -> str:
+        n = self._read_u64()
+        raw = self._mmap[self._cursor:self._cursor + n]
+        self._cursor += n
+        return raw.decode("utf-8")
+
+    def _read_metadata_value(self, value_type: int) -> Any:
+        if value_type in _SCALARS:
+            code, npdt = _SCALARS[value_type]
+            return self._take(code, np.dtype(npdt).itemsize)
+        if value_type == GGUF_METADATA_VALUE_TYPE_BOOL:
+            return self._take("<B", 1) != 0
+        if value_type == GGUF_METADATA_VALUE_TYPE_STRING:
+            return self._read_string()
+        if value_type == GGUF_METADATA_VALUE_TYPE_ARRAY:
+            item_type = self._read_u32()
+            count = self._read_u64()
+            if item_type in _SCALARS:
+                # Numeric arrays in one vectorised read; .tolist() yields the same
+                # Python ints/floats that per-item struct reads would.
+                npdt = np.dtype(_SCALARS[item_type][1])
+                if self._cursor + count * npdt.itemsize > len(self._mmap):
+                    raise struct.error("metadata array runs past the end of the file")
+                arr = np.frombuffer(self._mmap, dtype=npdt, count=count, offset=self._cursor)
+                self._cursor += count * npdt.itemsize
+                values = arr.tolist()
+                del arr
+                return values
+            if item_type == GGUF_METADATA_VALUE_TYPE_BOOL:
+                raw = self._mmap[self._cursor:self._cursor + count]
+                self._cursor += count
+                return [b != 0 for b in raw]
+            return [self._read_metadata_value(item_type) for _ in range(count)]
+        raise ValueError(f"Unknown metadata value type: {value_type}")
+
+    def _parse_header(self) -> None:
+        self._cursor = 0
+        magic = self._read_u32()
+        if magic != GGUF_MAGIC:
+            raise ValueError(f"Invalid GGUF magic: {hex(magic)}")
+        version = self._read_u32()
+        if version < 2 or version > 3:
+            raise ValueError(f"Unsupported GGUF version: {version}")
+        n_tensors = self._read_u64()
+        n_kv = self._read_u64()
+        hdr = GGUFHeader(magic=magic, version=version, n_tensors=n_tensors, n_kv=n_kv)
+        self._header = hdr
+        for _ in range(n_kv):
+            key = self._read_string()
+            hdr.metadata[key] = self._read_metadata_value(self._read_u32())
+        for _ in range(n_tensors):
+            name = self._read_string()
+            n_dims = self._read_u32()
+            dims = struct.unpack_from(f"<{n_dims}Q", self._mmap, self._cursor)
+            self._cursor += 8 * n_dims
+            ggml_type = self._read_u32()
+            offset = self._read_u64()
+            hdr.tensors[name] = GGUFTensorInfo(name=name, n_dims=n_dims, dims=tuple(dims), dtype=ggml_type,
+                                               offset=offset)
+        # The reference aligns the data section to a fixed 32 bytes (:321-323).
+        hdr.tensor_data_offset = (self._cursor + 31) // 32 * 32
+
+    # -- raw bytes ------------------------------------------------------------
+    def _extent(self, name: str) -> Tuple[GGUFTensorInfo, int, int]:
+        if name not in self.tensors:
+            raise KeyError(f"Tensor not found: {name}")
+        info = self.tensors[name]
+        start = self._header.tensor_data_offset + info.offset
+        return info, start, info.nbytes
+
+    def read_tensor_raw(self, name: str) -> bytes:
+        """Packed bytes of a tensor, undecoded (reference :325-333)."""
+        info, start, nbytes = self._extent(name)
+        return bytes(self._mmap[start:start + nbytes])
+
+    def _host_address(self, start: int, nbytes: int) -> int:
+        if start + nbytes > len(self._mmap):
+            raise ValueError(f"Data too short: {max(len(self._mmap) - start, 0)} < {nbytes}")
+        if self._view is None:
+            self._view = np.frombuffer(self._mmap, dtype=np.uint8)
+        return self._view.ctypes.data + start
+
+    # -- decode -----------------------------------------------------------------
+    def read_tensor(self, name: str, device: str = "cpu", dtype: torch.dtype = torch.float32, *,
+                    rows: Optional[Tuple[int, int]] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Decode one tensor on the GPU (reference :335-379).
+
+        Returns a new contiguous tensor of shape ``info.shape`` on ``device``
+        with ``dtype``; the values carry the reference's bits.  The decode is
+        queued on the current CUDA stream of the decoding device.
+
+        rows: decode only rows ``[start, stop)`` of the leading axis (a
+            tensor-parallel row shard); needs the row length to cover whole
+            32-element blocks for quantised types.
+        out: decode straight into this CUDA tensor (contiguous, matching
+            element count).  When ``out.dtype`` differs from ``dtype`` the
+            value is rounded to ``dtype`` first and then converted, exactly as
+            ``out.copy_(read_tensor(..., dtype=dtype))`` would.
+        """
+        info, start, nbytes = self._extent(name)
+        if info.dtype not in QUANT_INFO:   # unreachable after nbytes, kept for the reference's message (:371-374)
+            raise NotImplementedError(f"Dequantization not implemented for {info.dtype_name}")
+        shape = info.shape
+        numel = info.numel
+        if rows is not None:
+            r0, r1 = rows
+            if not shape or not (0 <= r0 <= r1 <= shape[0]):
+                raise ValueError(f"rows {rows} outside leading axis of shape {shape}")
+            row_elems = numel // shape[0] if shape[0] else 0
+            per_block, block_bytes = QUANT_INFO[info.dtype]
+            if row_elems % per_block:
+                raise ValueError(f"row length {row_elems} does not cover whole {per_block}-element blocks")
+            start += r0 * (row_elems // per_block) * block_bytes
+            numel = (r1 - r0) * row_elems
+            nbytes = numel // per_block * block_bytes
+            shape = (r1 - r0,) + tuple(shape[1:])
+
+        if out is not None:
+            if out.device.type != "cuda" or not out.is_contiguous() or out.numel() != numel:
+                raise ValueError("out must be a contiguous CUDA tensor with the decoded element count")
+            if out.dtype not in _TORCH_TO_OUT or dtype not in _TORCH_TO_OUT:
+                raise ValueError(f"unsupported dtype pair {dtype} -> {out.dtype}")
+            target = out
+            want = cuda_dev = out.device
+        else:
+            want, cuda_dev = _cuda_device_for(device)
+            if dtype not in _TORCH_TO_OUT:
+                # Other torch dtypes: decode to fp32 on the device, let torch cast (same rounding as .to()).
+                t32 = self.read_tensor(name, device=cuda_dev, dtype=torch.float32, rows=rows)
+                return t32.to(device=want, dtype=dtype)
+            target = torch.empty(shape, dtype=dtype, device=cuda_dev)
+        if numel:
+            host = self._host_address(start, nbytes)
+            with torch.cuda.device(cuda_dev):
+                _Stager.get(cuda_dev.index).submit(host, nbytes, info.dtype, _TORCH_TO_OUT[dtype],
+                                                   _TORCH_TO_OUT[target.dtype], target, numel)
+        if out is not None:
+            return out
+        return target if want.type == "cuda" else target.to(want)
+
+    def tensor_iterator(self, pattern: Optional[str] = None, device: str = "cpu",
+                        dtype: torch.dtype = torch.float32) -> Iterator[Tuple[str, torch.Tensor]]:
+        """(name, tensor) pairs in file order, optionally filtered by a glob (reference :381-400)."""
+        for name in self.tensors:
+            if pattern is not None and not fnmatch.fnmatch(name, pattern):
+                continue
+            yield name, self.read_tensor(name, device=device, dtype=dtype)
+
+
+# ---------------------------------------------------------------------------
+# Context managers (reference :561-660)
+# ---------------------------------------------------------------------------
+@contextmanager
+def tensor_loading_context(path: str | Path, device: str = "cpu",
+                           dtype: torch.dtype = torch.float32) -> Iterator[GGUFReader]:
+    """Yields an opened reader.  ``device``/``dtype`` are accepted and unused, as in the reference (:561-575)."""
+    with GGUFReader(path) as reader:
+        yield reader
+
+
+class StreamingDequantizer:
+    """Streams decoded tensors to the GPU in batches (reference :603-660)."""
+
+    def __init__(self, path: str | Path, batch_size: int = 4, device: str = "cuda",
+                 dtype: torch.dtype = torch.float16):
+        self.path = Path(path)
+        self.batch_size = batch_size
+        self.device = device
+        self.dtype = dtype
+        self._reader: Optional[GGUFReader] = None
+
+    def open(self):
+        self._reader = GGUFReader(self.path)
+        self._reader.__enter__()
+
+    def close(self):
+        if self._reader:
+            self._reader.__exit__(None, None, None)
+            self._reader = None
+
+    def _need_reader(self) -> GGUFReader:
+        if self._reader is None:
+            raise RuntimeError("Streamer not opened")
+        return self._reader
+
+    @property
+    def tensor_names(self) -> List[str]:
+        return list(self._need_reader().tensors.keys())
+
+    def iter_batches(self) -> Iterator[Dict[str, torch.Tensor]]:
+        """Dicts of ``batch_size`` tensors in file order.  Each yielded tensor is
+        the caller's; later batches never alias it."""
+        reader = self._need_reader()
+        names = self.tensor_names
+        for i in range(0, len(names), self.batch_size):
+            yield {n: reader.read_tensor(n, device=self.device, dtype=self.dtype) for n in names[i:i + self.batch_size]}
+
+    def iter_tensors(self) -> Iterator[Tuple[str, torch.Tensor]]:
+        reader = self._need_reader()
+        for name in self.tensor_names:
+            yield name, reader.read_tensor(name, device=self.device, dtype=self.dtype)
+
+
+@contextmanager
+def streaming_dequant_context(path: str | Path, batch_size: int = 4, device: str = "cuda",
+                              dtype: torch.dtype = torch.float16) -> Iterator[StreamingDequantizer]:
+    streamer = StreamingDequantizer(path, batch_size, device, dtype)
+    streamer.open()
+    try:
+        yield streamer
+    finally:
+        streamer.close()
+
+
+# ---------------------------------------------------------------------------
+# Model patcher (reference :667-774)
+# ---------------------------------------------------------------------------
+class GGUFModelPatcher:
+    """Writes GGUF tensors into the parameters of a torch module."""
+
+    def __init__(self, gguf_path: str | Path, name_mapping: Optional[Dict[str, str]] = None):
+        self.gguf_path = Path(gguf_path)
+        self.name_mapping = name_mapping or {}
+        self._reader: Optional[GGUFReader] = None
+
+    def _map_name(self, gguf_name: str) -> str:
+        """Explicit mapping first, else drop a leading ``model.`` (reference :689-702)."""
+        mapped = self.name_mapping.get(gguf_name)
+        if mapped is not None:
+            return mapped
+        return gguf_name[6:] if gguf_name.startswith("model.") else gguf_name
+
+    @contextmanager
+    def patch_context(self, model: torch.nn.Module, device: str = "cuda", dtype: torch.dtype = torch.float16,
+                      strict: bool = False, *, shard: Optional[Tuple[int, int]] = None,
+                      replicate_group=None) -> Iterator[Dict[str, Any]]:
+        """Loads every mapped tensor into ``model`` before yielding the stats dict
+        ``{"loaded", "skipped", "missing", "unexpected"}`` (reference :704-774).
+
+        Each value is rounded to ``dtype`` and then converted to the parameter's
+        dtype, which is what ``param.copy_(read_tensor(..., dtype=dtype))`` does;
+        CUDA parameters are written in place by the decode kernel.
+
+        shard=(rank, world_size): tensors with two or more axes are row-sharded;
+            a parameter whose leading axis is ``rows // world_size`` receives
+            rows ``[rank*rows/W, (rank+1)*rows/W)`` only.  One-axis tensors are
+            replicated.
+        replicate_group: a ``torch.distributed`` process group.  With ``shard``,
+            parameters that hold the full shape are filled by decoding only this
+            rank's rows and all-gathering the rest over the group (NCCL).
+        """
+        from .sharding import row_range
+
+        stats: Dict[str, Any] = {"loaded": 0, "skipped": 0, "missing": [], "unexpected": []}
+        params = dict(model.named_parameters())
+        gathers = []
+        with GGUFReader(self.gguf_path) as reader:
+            self._reader = reader
+            for gguf_name, info in reader.tensors.items():
+                torch_name = self._map_name(gguf_name)
+                if torch_name not in params:
+                    stats["unexpected"].append(gguf_name)
+                    stats["skipped"] += 1
+                    continue
+                param = params[torch_name]
+                full_shape = tuple(info.shape)
+                rows = None
+                gather = False
+                if shard is not None and len(full_shape) >= 2:
+                    rank, world = shard
+                    r0, r1 = row_range(full_shape[0], rank, world)
+                    if tuple(param.shape) == (r1 - r0,) + full_shape[1:]:
+                        rows = (r0, r1)
+                    elif replicate_group is not None and tuple(param.shape) == full_shape:
+                        rows, gather = (r0, r1), True
+                expect = full_shape if (rows is None or gather) else (rows[1] - rows[0],) + full_shape[1:]
+                if tuple(param.shape) != expect:
+                    logger.warning(f"Shape mismatch for {torch_name}: GGUF {torch.Size(expect)} vs Model {param.shape}")
+                    stats["skipped"] += 1
+                    continue
+                with torch.no_grad():
+                    direct = (param.device.type == "cuda" and param.is_contiguous()
+                              and param.dtype in _TORCH_TO_OUT and dtype in _TORCH_TO_OUT)
+                    if direct:
+                        dst = param.data
+                        if gather:
+                            dst = dst[rows[0]:rows[1]]
+                        reader.read_tensor(gguf_name, dtype=dtype, rows=rows, out=dst)
+                    else:
+                        tensor = reader.read_tensor(gguf_name, device=device, dtype=dtype, rows=rows)
+                        if gather:
+                            param.data[rows[0]:rows[1]].copy_(tensor)
+                        else:
+                            param.copy_(tensor)
+                    if gather:
+                        gathers.append(param.data)
+                stats["loaded"] += 1
+
+            if gathers:
+                from .sharding import all_gather_rows
+                for full in gathers:
+                    all_gather_rows(full, replicate_group)
+
+            mapped = {self._map_name(n) for n in reader.tensors}
+            stats["missing"] = [n for n in params if n not in mapped]
+            if strict and stats["missing"]:
+                raise ValueError(f"Missing parameters in GGUF: {stats['missing'][:10]}...")
+            # Packed bytes have left the mmap once submit returns; the decodes are
+            # ordered on the current stream, so the parameters are ready for any
+            # work the caller queues next.
+            yield stats
+            self._reader = None
+
+
+# ---------------------------------------------------------------------------
+# Convenience functions (reference :781-844)
+# ---------------------------------------------------------------------------
+def load_gguf_tensors(path: str | Path, device: str = "cpu", dtype: torch.dtype = torch.float32) -> Dict[str, torch.Tensor]:
+    """All tensors of a file, decoded (reference :781-796)."""
+    with GGUFReader(path) as reader:
+        return {name: reader.read_tensor(name, device=device, dtype=dtype) for name in reader.tensors}
+
+
+def inspect_gguf(path: str | Path) -> Dict[str, Any]:
+    """File summary without decoding anything (reference :799-818)."""
+    with GGUFReader(path) as reader:
+        listing = {name: {"shape": t.shape, "dtype": t.dtype_name, "numel": t.numel, "nbytes": t.nbytes}
+                   for name, t in reader.tensors.items()}
+        return {"version": reader.header.version, "n_tensors": reader.header.n_tensors,
+                "metadata": reader.header.metadata, "tensors": listing}
+
+
+def print_gguf_info(path: str | Path):
+    """Human-readable summary (reference :821-844)."""
+    info = inspect_gguf(path)
+    print(f"GGUF File: {path}")
+    print(f"Version: {info['version']}")
+    print(f"Tensors: {info['n_tensors']}")
+    print()
+    print("Metadata:")
+    for key in ("general.architecture", "general.name", "general.file_type"):
+        if key in info["metadata"]:
+            print(f"  {key}: {info['metadata'][key]}")
+    print()
+    print("Tensors (first 20):")
+    for i, (name, t) in enumerate(info["tensors"].items()):
+        if i >= 20:
+            print(f"  ... and {len(info['tensors']) - 20} more")
+            break
+        print(f"  {name}: {t['shape']} ({t['dtype']}, {t['nbytes'] / 1024 / 1024:.2f} MB)")

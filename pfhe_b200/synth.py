@@ -1,0 +1,235 @@
+"""Synthetic GGUF files and tensors with seeded contents.
+
+Real checkpoints are not available offline, so tests and benchmarks use files
+that have the layout the parser expects (reference
+src/phfe/inference/gguf_loader.py:275-323: magic, version, tensor and
+key/value counts, key/values, tensor infos, data at the next 32-byte boundary,
+every tensor 32-byte aligned) and the tensor names, shapes and type mix of
+Llama-style models (names as in the reference's src/phfe/inference/model.py:381-416).
+Block contents are random with the distributions the benchmark configuration
+states; no weights of any real model are reproduced.
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+from typing import Any, BinaryIO, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .gguf_loader import (GGML_TYPE_BF16, GGML_TYPE_F16, GGML_TYPE_F32, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1,
+                          GGML_TYPE_Q8_0, GGUF_MAGIC, QUANT_INFO)
+
+ALIGNMENT = 32
+
+
+# ---------------------------------------------------------------------------
+# Packed tensor contents
+# ---------------------------------------------------------------------------
+def packed_nbytes(ggml_type: int, numel: int) -> int:
+    per_block, block_bytes = QUANT_INFO[ggml_type]
+    return -(-numel // per_block) * block_bytes
+
+
+def random_packed(ggml_type: int, numel: int, rng: np.random.Generator, scale: Optional[float] = None) -> np.ndarray:
+    """uint8 array holding ``numel`` elements of ``ggml_type``.
+
+    Q8_0: d = |N(0,1)|*0.01 as fp16, quants uniform in [-127, 127].
+    Q4_0: d = |N(0,1)|*0.02 as fp16, nibbles uniform in 0..15.
+    Q4_1: as Q4_0 plus m = N(0, 0.01) as fp16 (0.01 is the standard deviation).
+    F32 / F16 / BF16: 1 + 0.05*N(0,1) (norm-weight-like values).
+    """
+    per_block, block_bytes = QUANT_INFO[ggml_type]
+    n_blocks = -(-numel // per_block)
+    if ggml_type in (GGML_TYPE_F32, GGML_TYPE_F16, GGML_TYPE_BF16):
+        vals = (1.0 + 0.05 * rng.standard_normal(numel, dtype=np.float32)).astype(np.float32)
+        if ggml_type == GGML_TYPE_F32:
+            return vals.view(np.uint8)
+        if ggml_type == GGML_TYPE_F16:
+            return vals.astype(np.float16).view(np.uint8)
+        return (vals.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8)   # truncated bf16 is fine for inputs
+    out = np.empty((n_blocks, block_bytes), dtype=np.uint8)
+    if ggml_type == GGML_TYPE_Q8_0:
+        s = 0.01 if scale is None else scale
+        out[:, 0:2] = (np.abs(rng.standard_normal(n_blocks, dtype=np.float32)) * s).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+        out[:, 2:] = rng.integers(-127, 128, size=(n_blocks, 32), dtype=np.int8).view(np.uint8)
+    else:
+        s = 0.02 if scale is None else scale
+        out[:, 0:2] = (np.abs(rng.standard_normal(n_blocks, dtype=np.float32)) * s).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+        qs = 2
+        if ggml_type == GGML_TYPE_Q4_1:
+            out[:, 2:4] = (rng.standard_normal(n_blocks, dtype=np.float32) * 0.01).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+            qs = 4
+        out[:, qs:] = rng.integers(0, 256, size=(n_blocks, 16), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+# ---------------------------------------------------------------------------
+# Writer
+# ---------------------------------------------------------------------------
+_KV_TYPES = {"u8": (0, "<B"), "i8": (1, "<b"), "u16": (2, "<H"), "i16": (3, "<h"), "u32": (4, "<I"), "i32": (5, "<i"),
+             "f32": (6, "<f"), "bool": (7, "<B"), "str": (8, None), "u64": (10, "<Q"), "i64": (11, "<q"),
+             "f64": (12, "<d")}
+
+
+def _enc_str(s: str) -> bytes:
+    b = s.encode("utf-8")
+    return struct.pack("<Q", len(b)) + b
+
+
+def _enc_value(kind: str, value: Any) -> bytes:
+    """``kind`` is a scalar kind from _KV_TYPES or ``"arr:<kind>"``."""
+    if kind.startswith("arr:"):
+        item = kind[4:]
+        tid = 9 if item.startswith("arr:") else _KV_TYPES[item][0]
+        body = b"".join(_enc_item(item, v) for v in value)
+        return struct.pack("<I", 9) + struct.pack("<IQ", tid, len(value)) + body
+    return struct.pack("<I", _KV_TYPES[kind][0]) + _enc_item(kind, value)
+
+
+def _enc_item(kind: str, value: Any) -> bytes:
+    if kind.startswith("arr:"):
+        item = kind[4:]
+        tid = 9 if item.startswith("arr:") else _KV_TYPES[item][0]
+        return struct.pack("<IQ", tid, len(value)) + b"".join(_enc_item(item, v) for v in value)
+    if kind == "str":
+        return _enc_str(value)
+    if kind == "bool":
+        return struct.pack("<B", 1 if value else 0)
+    return struct.pack(_KV_TYPES[kind][1], value)
+
+
+@dataclass
+class TensorSpec:
+    name: str
+    shape: Tuple[int, ...]          # torch order (rows first); stored reversed as ggml dims
+    ggml_type: int
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+    @property
+    def nbytes(self) -> int:
+        return packed_nbytes(self.ggml_type, self.numel)
+
+
+def _align(n: int) -> int:
+    return (n + ALIGNMENT - 1) // ALIGNMENT * ALIGNMENT
+
+
+def header_bytes(specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str, Any]], version: int = 3) -> Tuple[bytes, List[int]]:
+    """Header + key/values + tensor infos, and each tensor's offset in the data section."""
+    out = [struct.pack("<IIQQ", GGUF_MAGIC, version, len(specs), len(metadata))]
+    for key, kind, value in metadata:
+        out.append(_enc_str(key))
+        out.append(_enc_value(kind, value))
+    offsets, cur = [], 0
+    for sp in specs:
+        offsets.append(cur)
+        dims = tuple(reversed(sp.shape))
+        out.append(_enc_str(sp.name))
+        out.append(struct.pack("<I", len(dims)))
+        out.append(struct.pack(f"<{len(dims)}Q", *dims))
+        out.append(struct.pack("<IQ", sp.ggml_type, cur))
+        cur = _align(cur + sp.nbytes)
+    return b"".join(out), offsets
+
+
+def write_gguf(path, specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str, Any]] = (),
+               seed: int = 0, contents: Optional[Dict[str, np.ndarray]] = None, version: int = 3,
+               chunk_elems: int = 1 << 26) -> int:
+    """Writes a GGUF file; returns its size.  Tensors not in ``contents`` get
+    seeded random blocks, generated in chunks so that multi-gigabyte tensors
+    never sit in memory whole."""
+    head, offsets = header_bytes(specs, metadata, version)
+    data_start = _align(len(head))
+    with open(path, "wb") as f:
+        f.write(head)
+        f.write(b"\0" * (data_start - len(head)))
+        for i, (sp, off) in enumerate(zip(specs, offsets)):
+            assert f.tell() == data_start + off
+            if contents is not None and sp.name in contents:
+                raw = np.ascontiguousarray(contents[sp.name]).view(np.uint8).reshape(-1)
+                assert raw.size == sp.nbytes, (sp.name, raw.size, sp.nbytes)
+                f.write(raw.tobytes())
+            else:
+                rng = np.random.default_rng([seed, i])
+                per_block = QUANT_INFO[sp.ggml_type][0]
+                step = max(chunk_elems // per_block * per_block, per_block)
+                for e0 in range(0, sp.numel, step):
+                    f.write(random_packed(sp.ggml_type, min(step, sp.numel - e0), rng).tobytes())
+            pad = _align(f.tell() - data_start) - (f.tell() - data_start)
+            if pad and i + 1 < len(specs):
+                f.write(b"\0" * pad)
+        return f.tell()
+
+
+# ---------------------------------------------------------------------------
+# Llama-shaped model files
+# ---------------------------------------------------------------------------
+@dataclass
+class LlamaShape:
+    name: str
+    n_layers: int
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    linear_type: int
+    embed_type: int = GGML_TYPE_Q8_0
+    norm_type: int = GGML_TYPE_F32
+
+
+LLAMA2_7B = LlamaShape("llama2-7b-q4_0", 32, 4096, 32, 32, 128, 11008, 32000, GGML_TYPE_Q4_0)
+LLAMA3_70B = LlamaShape("llama3-70b-q4_1", 80, 8192, 64, 8, 128, 28672, 128256, GGML_TYPE_Q4_1)
+
+
+def llama_specs(m: LlamaShape, n_layers: Optional[int] = None) -> List[TensorSpec]:
+    """Tensor list of a Llama-style file in the order llama.cpp converters emit."""
+    L = m.n_layers if n_layers is None else n_layers
+    q_out, kv_out = m.n_heads * m.head_dim, m.n_kv_heads * m.head_dim
+    specs = [TensorSpec("token_embd.weight", (m.vocab, m.hidden), m.embed_type)]
+    for i in range(L):
+        p = f"blk.{i}."
+        specs += [
+            TensorSpec(p + "attn_norm.weight", (m.hidden,), m.norm_type),
+            TensorSpec(p + "attn_q.weight", (q_out, m.hidden), m.linear_type),
+            TensorSpec(p + "attn_k.weight", (kv_out, m.hidden), m.linear_type),
+            TensorSpec(p + "attn_v.weight", (kv_out, m.hidden), m.linear_type),
+            TensorSpec(p + "attn_output.weight", (m.hidden, q_out), m.linear_type),
+            TensorSpec(p + "ffn_norm.weight", (m.hidden,), m.norm_type),
+            TensorSpec(p + "ffn_gate.weight", (m.ffn, m.hidden), m.linear_type),
+            TensorSpec(p + "ffn_up.weight", (m.ffn, m.hidden), m.linear_type),
+            TensorSpec(p + "ffn_down.weight", (m.hidden, m.ffn), m.linear_type),
+        ]
+    specs += [TensorSpec("output_norm.weight", (m.hidden,), m.norm_type),
+              TensorSpec("output.weight", (m.vocab, m.hidden), m.embed_type)]
+    return specs
+
+
+def llama_metadata(m: LlamaShape, n_layers: Optional[int] = None) -> List[Tuple[str, str, Any]]:
+    L = m.n_layers if n_layers is None else n_layers
+    return [
+        ("general.architecture", "str", "llama"),
+        ("general.name", "str", f"synthetic-{m.name}"),
+        ("general.file_type", "u32", 2),
+        ("llama.block_count", "u32", L),
+        ("llama.embedding_length", "u32", m.hidden),
+        ("llama.attention.head_count", "u32", m.n_heads),
+        ("llama.attention.head_count_kv", "u32", m.n_kv_heads),
+        ("llama.feed_forward_length", "u32", m.ffn),
+        ("llama.context_length", "u32", 4096),
+        ("llama.vocab_size", "u32", m.vocab),
+        ("llama.attention.layer_norm_rms_epsilon", "f32", 1e-5),
+        ("llama.rope.freq_base", "f32", 10000.0),
+    ]
+
+
+def write_llama_gguf(path, m: LlamaShape, n_layers: Optional[int] = None, seed: int = 0) -> int:
+    return write_gguf(path, llama_specs(m, n_layers), llama_metadata(m, n_layers), seed=seed)

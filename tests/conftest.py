@@ -1,0 +1,64 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+F32, F16, Q4_0, Q4_1, Q8_0, BF16 = 0, 1, 2, 3, 8, 30
+FORMATS = {"Q4_0": Q4_0, "Q4_1": Q4_1, "Q8_0": Q8_0, "F16": F16, "BF16": BF16, "F32": F32}
+OUT_DTYPES = ("f32", "f16", "bf16")
+CAST2 = (("f16", "bf16"), ("bf16", "f16"), ("f16", "f32"), ("bf16", "f32"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+def load_golden(fmt_name: str):
+    return np.load(os.path.join(GOLDEN, f"decode_{fmt_name}.npz"))
+
+
+def as_bits(a: np.ndarray) -> np.ndarray:
+    """Raw bit patterns of a float32 / float16 / uint16 array."""
+    if a.dtype == np.float32:
+        return a.view(np.uint32)
+    if a.dtype == np.float16:
+        return a.view(np.uint16)
+    return a
+
+
+def is_nan_bits(b: np.ndarray) -> np.ndarray:
+    if b.dtype == np.uint32:
+        return (b & 0x7FFFFFFF) > 0x7F800000
+    raise TypeError(b.dtype)
+
+
+def nan_mask(bits: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype == "f32":
+        return (bits & 0x7FFFFFFF) > 0x7F800000
+    if dtype == "f16":
+        return (bits & 0x7FFF) > 0x7C00
+    return (bits & 0x7FFF) > 0x7F80
+
+
+def assert_same_bits(got: np.ndarray, want: np.ndarray, dtype: str, what: str = ""):
+    """Bit-exact for every non-NaN value; NaN must meet NaN (payloads may differ)."""
+    got, want = as_bits(got).reshape(-1), as_bits(want).reshape(-1)
+    assert got.shape == want.shape, f"{what}: {got.shape} vs {want.shape}"
+    gn, wn = nan_mask(got, dtype), nan_mask(want, dtype)
+    assert np.array_equal(gn, wn), f"{what}: NaN positions differ"
+    bad = (got != want) & ~wn
+    if bad.any():
+        i = int(np.flatnonzero(bad)[0])
+        raise AssertionError(f"{what}: {int(bad.sum())} mismatches, first at {i}: got {got[i]:#x} want {want[i]:#x}")
+
+
+@pytest.fixture(scope="session")
+def golden_dir():
+    return GOLDEN

@@ -1,0 +1,165 @@
+"""Generates the golden vectors in this directory by RUNNING THE REFERENCE.
+
+Usage (needs the reference checkout; not needed to run the tests):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It imports ``phfe.inference.gguf_loader`` from ``<reference>/src`` and records,
+for seeded inputs, the outputs of the reference's own decode functions
+(gguf_loader.py:407-554) followed by ``torch.Tensor.to(dtype)`` (:377-378), and
+of its header parser (:275-323) on a small file written by
+``pfhe_b200.synth``.  Outputs are stored as raw bit patterns.
+
+Files written:
+  decode_<FMT>.npz   packed input bytes + reference outputs (f32/f16/bf16 bits,
+                     and the two-step roundings patch_context performs)
+  mini.gguf          7-tensor file covering all six types and every metadata kind
+  mini_expected.json what the reference's GGUFReader parsed from mini.gguf
+  mini_tensors.npz   reference read_tensor(...) of every tensor in mini.gguf
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import warnings
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+F32, F16, Q4_0, Q4_1, Q8_0, BF16 = 0, 1, 2, 3, 8, 30
+NAMES = {F32: "F32", F16: "F16", BF16: "BF16", Q4_0: "Q4_0", Q4_1: "Q4_1", Q8_0: "Q8_0"}
+TORCH = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+CAST2 = [("f16", "bf16"), ("bf16", "f16"), ("f16", "f32"), ("bf16", "f32")]
+
+# fp16 bit patterns worth pinning: zeros, subnormal ends, normal ends, ones, inf, a NaN
+SPECIAL_F16 = [0x0000, 0x8000, 0x0001, 0x8001, 0x03FF, 0x0400, 0x3C00, 0xBC00, 0x7BFF, 0xFBFF, 0x7C00, 0xFC00, 0x7E00,
+               0x1400, 0x9400, 0x5640, 0x2E66]
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.float32:
+        return t.numpy().view(np.uint32).copy()
+    return t.view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def quant_case(fmt: int, rng: np.random.Generator):
+    """Packed blocks: specials x extreme nibble patterns, then random finite scales."""
+    bb = {Q4_0: 18, Q4_1: 20, Q8_0: 34}[fmt]
+    blocks = []
+    fills = [0x00, 0xFF, 0x88, 0x80, 0x08, 0x7F, 0x81, 0xF0]
+    for i, s in enumerate(SPECIAL_F16):
+        b = np.zeros(bb, dtype=np.uint8)
+        b[0:2] = np.array([s], dtype=np.uint16).view(np.uint8)
+        o = 2
+        if fmt == Q4_1:
+            b[2:4] = np.array([SPECIAL_F16[(i * 5 + 3) % len(SPECIAL_F16)]], dtype=np.uint16).view(np.uint8)
+            o = 4
+        b[o:] = fills[i % len(fills)]
+        blocks.append(b)
+        b2 = b.copy()
+        b2[o:] = rng.integers(0, 256, bb - o, dtype=np.uint8)
+        blocks.append(b2)
+    n_rand = 200
+    r = rng.integers(0, 256, size=(n_rand, bb), dtype=np.uint8)
+    # random scale/min bit patterns, finite only (exponent field != 31)
+    for col in ([0] if fmt != Q4_1 else [0, 2]):
+        h = rng.integers(0, 1 << 16, n_rand, dtype=np.uint16)
+        h = np.where((h & 0x7C00) == 0x7C00, h & 0xBFFF, h).astype(np.uint16)
+        r[:, col:col + 2] = h.view(np.uint8).reshape(n_rand, 2)
+    # a run of "realistic" blocks too
+    small = (np.abs(rng.standard_normal(32).astype(np.float32)) * 0.02).astype(np.float16)
+    r[:32, 0:2] = small.view(np.uint8).reshape(32, 2)
+    blocks.extend(list(r))
+    raw = np.concatenate(blocks)
+    numel = len(blocks) * 32 - 5          # ragged tail: the last block is cut (output[:numel])
+    return raw, numel
+
+
+def elem_case(fmt: int, rng: np.random.Generator):
+    n = 4099
+    if fmt == F32:
+        u = rng.integers(0, 1 << 32, n, dtype=np.uint64).astype(np.uint32)
+        # keep most values in fp16/bf16-interesting ranges: exponent 90..150
+        e = rng.integers(90, 151, n, dtype=np.uint32)
+        u[: n - 64] = (u[: n - 64] & 0x807FFFFF) | (e[: n - 64] << 23)
+        u[-8:] = np.array([0, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00000, 0x477FE000, 0x477FF000, 0x33000000], dtype=np.uint32)
+        return u.view(np.uint8), n
+    u = rng.integers(0, 1 << 16, n, dtype=np.uint16)
+    u[-len(SPECIAL_F16):] = np.array(SPECIAL_F16, dtype=np.uint16)
+    return u.view(np.uint8), n
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, os.path.join(ref_root, "src"))
+    import phfe.inference.gguf_loader as ref
+
+    decode = {F32: ref._decode_f32, F16: ref._decode_f16, BF16: ref._decode_bf16,
+              Q4_0: ref._dequantize_q4_0, Q4_1: ref._dequantize_q4_1, Q8_0: ref._dequantize_q8_0}
+    warnings.simplefilter("ignore")
+    rng = np.random.default_rng(20240607)
+    for fmt in (Q4_0, Q4_1, Q8_0, F16, BF16, F32):
+        raw, numel = quant_case(fmt, rng) if fmt in (Q4_0, Q4_1, Q8_0) else elem_case(fmt, rng)
+        t32 = decode[fmt](raw.tobytes(), numel)
+        assert t32.dtype == torch.float32 and t32.numel() == numel
+        out = {"raw": raw, "numel": np.int64(numel), "f32": bits(t32)}
+        for k in ("f16", "bf16"):
+            out[k] = bits(t32.to(TORCH[k]))
+        for mid, fin in CAST2:
+            out[f"{mid}_then_{fin}"] = bits(t32.to(TORCH[mid]).to(TORCH[fin]))
+        np.savez_compressed(os.path.join(HERE, f"decode_{NAMES[fmt]}.npz"), **out)
+        print(NAMES[fmt], numel, "elements")
+
+    # --- a small file through the reference's parser and read_tensor ---------
+    from pfhe_b200 import synth
+    specs = [
+        synth.TensorSpec("token_embd.weight", (48, 64), Q8_0),
+        synth.TensorSpec("blk.0.attn_norm.weight", (64,), F32),
+        synth.TensorSpec("blk.0.attn_q.weight", (64, 64), Q4_0),
+        synth.TensorSpec("blk.0.ffn_up.weight", (96, 64), Q4_1),
+        synth.TensorSpec("blk.0.half.weight", (3, 5, 32), F16),
+        synth.TensorSpec("model.blk.0.bf.weight", (7, 32), BF16),
+        synth.TensorSpec("ragged.weight", (50,), Q8_0),
+    ]
+    meta = [
+        ("general.architecture", "str", "llama"),
+        ("general.name", "str", "mini é中"),
+        ("general.file_type", "u32", 2),
+        ("t.u8", "u8", 200), ("t.i8", "i8", -100), ("t.u16", "u16", 65000), ("t.i16", "i16", -30000),
+        ("t.i32", "i32", -2000000000), ("t.u64", "u64", 2 ** 63 + 5), ("t.i64", "i64", -2 ** 62),
+        ("t.f32", "f32", 1.5), ("t.f64", "f64", 1e-300), ("t.true", "bool", True), ("t.false", "bool", False),
+        ("tokenizer.ggml.tokens", "arr:str", ["<s>", "</s>", "a", "é", ""]),
+        ("tokenizer.ggml.scores", "arr:f32", [0.0, -1.5, 2.25]),
+        ("tokenizer.ggml.token_type", "arr:i32", [1, 2, 3, -4]),
+        ("t.flags", "arr:bool", [True, False, True]),
+        ("t.nested", "arr:arr:u16", [[1, 2], [], [3]]),
+        ("general.alignment", "u32", 64),       # the reference ignores this key and aligns to 32
+    ]
+    path = os.path.join(HERE, "mini.gguf")
+    synth.write_gguf(path, specs, meta, seed=7)
+    with ref.GGUFReader(path) as r:
+        expected = {
+            "version": r.header.version, "n_tensors": r.header.n_tensors, "n_kv": r.header.n_kv,
+            "tensor_data_offset": r.header.tensor_data_offset,
+            "metadata": r.metadata,
+            "tensors": {n: {"n_dims": t.n_dims, "dims": list(t.dims), "dtype": t.dtype, "offset": t.offset,
+                            "shape": list(t.shape), "numel": t.numel, "nbytes": t.nbytes, "dtype_name": t.dtype_name}
+                        for n, t in r.tensors.items()},
+        }
+        tens = {}
+        for n in r.tensors:
+            for k, dt in TORCH.items():
+                tens[f"{n}|{k}"] = bits(r.read_tensor(n, device="cpu", dtype=dt).reshape(-1))
+            tens[f"{n}|raw"] = np.frombuffer(r.read_tensor_raw(n), dtype=np.uint8)
+    with open(os.path.join(HERE, "mini_expected.json"), "w") as f:
+        json.dump(expected, f, indent=1, ensure_ascii=True)
+    np.savez_compressed(os.path.join(HERE, "mini_tensors.npz"), **tens)
+    print("mini.gguf", os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,56 @@
+"""Helpers for the GPU parity tests: call the C ABI on torch-owned device memory."""
+import ctypes
+
+import numpy as np
+import torch
+
+from pfhe_b200 import _native
+
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+OUT_ID = {"f32": _native.OUT_F32, "f16": _native.OUT_F16, "bf16": _native.OUT_BF16}
+NP_BITS = {"f32": np.uint32, "f16": np.uint16, "bf16": np.uint16}
+
+
+def to_bits(t: torch.Tensor) -> np.ndarray:
+    t = t.detach().reshape(-1).cpu()
+    if t.dtype == torch.float32:
+        return t.numpy().view(np.uint32)
+    return t.view(torch.int16).numpy().view(np.uint16)
+
+
+def device_bytes(raw: np.ndarray, skew: int = 0) -> torch.Tensor:
+    """Packed bytes on the GPU, starting `skew` bytes past a 256-byte aligned address."""
+    buf = torch.empty(raw.size + skew + 64, dtype=torch.uint8, device="cuda")
+    view = buf[skew:skew + raw.size]
+    view.copy_(torch.from_numpy(np.ascontiguousarray(raw)))
+    return view
+
+
+def decode_on_gpu(ggml_type: int, raw: np.ndarray, numel: int, out: str, mid: str | None = None, skew: int = 0,
+                  dst_skew_elems: int = 0, cfg: dict | None = None, src: torch.Tensor | None = None) -> torch.Tensor:
+    """One pfhe_dequant_launch[_ex] call; returns the output tensor (with guard elements checked)."""
+    L = _native.lib()
+    src = device_bytes(raw, skew) if src is None else src
+    guard = 64
+    full = torch.full((numel + dst_skew_elems + 2 * guard,), 0, dtype=TORCH_DT[out], device="cuda")
+    full.view(torch.int16 if out != "f32" else torch.int32).fill_(0x5A5A if out != "f32" else 0x5A5A5A5A)
+    dst = full[guard + dst_skew_elems: guard + dst_skew_elems + numel]
+    stream = torch.cuda.current_stream().cuda_stream
+    mid_id = OUT_ID[mid if mid is not None else out]
+    if cfg is None:
+        rc = L.pfhe_dequant_launch_cast2(ggml_type, mid_id, OUT_ID[out], src.data_ptr(), src.numel(),
+                                         dst.data_ptr(), numel * dst.element_size(), numel, stream)
+    else:
+        c = _native.LaunchCfg(streaming_stores=-1)
+        for k, v in cfg.items():
+            setattr(c, k, v)
+        rc = L.pfhe_dequant_launch_ex(ggml_type, mid_id, OUT_ID[out], src.data_ptr(), src.numel(),
+                                      dst.data_ptr(), numel * dst.element_size(), numel, stream, ctypes.byref(c))
+    _native.check(rc)
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    pat = 0x5A5A if out != "f32" else 0x5A5A5A5A
+    fb = to_bits(full)
+    lo = guard + dst_skew_elems
+    assert (fb[:lo] == pat).all() and (fb[lo + numel:] == pat).all(), "kernel wrote outside its destination"
+    return dst

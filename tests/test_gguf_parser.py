@@ -1,0 +1,166 @@
+"""Host logic: the Python header parser and the drop-in API surface (no GPU)."""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+import pfhe_b200
+from pfhe_b200 import gguf_loader as gl
+from pfhe_b200 import synth
+
+
+def _expected(golden_dir):
+    with open(os.path.join(golden_dir, "mini_expected.json")) as f:
+        return json.load(f)
+
+
+def test_parser_matches_reference_parse(golden_dir):
+    exp = _expected(golden_dir)
+    with gl.GGUFReader(os.path.join(golden_dir, "mini.gguf")) as r:
+        assert r.header.magic == gl.GGUF_MAGIC
+        assert r.header.version == exp["version"]
+        assert r.header.n_tensors == exp["n_tensors"] and r.header.n_kv == exp["n_kv"]
+        assert r.header.tensor_data_offset == exp["tensor_data_offset"]
+        assert list(r.metadata) == list(exp["metadata"])
+        for k, v in exp["metadata"].items():
+            assert r.metadata[k] == v and type(r.metadata[k]) is type(v), k
+        assert list(r.tensors) == list(exp["tensors"])
+        for n, e in exp["tensors"].items():
+            t = r.tensors[n]
+            assert (t.n_dims, list(t.dims), t.dtype, t.offset) == (e["n_dims"], e["dims"], e["dtype"], e["offset"])
+            assert (list(t.shape), t.numel, t.nbytes, t.dtype_name) == (e["shape"], e["numel"], e["nbytes"], e["dtype_name"])
+
+
+def test_raw_bytes_match_reference(golden_dir):
+    tens = np.load(os.path.join(golden_dir, "mini_tensors.npz"))
+    with pfhe_b200.tensor_loading_context(os.path.join(golden_dir, "mini.gguf")) as r:
+        for n in r.tensors:
+            assert r.read_tensor_raw(n) == tens[f"{n}|raw"].tobytes()
+        with pytest.raises(KeyError, match="Tensor not found"):
+            r.read_tensor_raw("nope")
+        with pytest.raises(KeyError, match="Tensor not found"):
+            r.read_tensor("nope")
+
+
+def test_not_opened_errors(golden_dir):
+    r = gl.GGUFReader(os.path.join(golden_dir, "mini.gguf"))
+    with pytest.raises(RuntimeError, match="File not opened"):
+        r.header
+    s = gl.StreamingDequantizer(os.path.join(golden_dir, "mini.gguf"))
+    for call in (lambda: s.tensor_names, lambda: next(s.iter_batches()), lambda: next(s.iter_tensors())):
+        with pytest.raises(RuntimeError, match="Streamer not opened"):
+            call()
+    s.open()
+    assert s.tensor_names[0] == "token_embd.weight"
+    s.close()
+    s.close()
+
+
+def test_bad_magic_and_version(tmp_path):
+    p = tmp_path / "bad.gguf"
+    p.write_bytes(struct.pack("<IIQQ", 0x12345678, 3, 0, 0))
+    with pytest.raises(ValueError, match="Invalid GGUF magic"):
+        with gl.GGUFReader(p):
+            pass
+    for v in (1, 4):
+        p.write_bytes(struct.pack("<IIQQ", gl.GGUF_MAGIC, v, 0, 0))
+        with pytest.raises(ValueError, match="Unsupported GGUF version"):
+            with gl.GGUFReader(p):
+                pass
+    p.write_bytes(struct.pack("<IIQQ", gl.GGUF_MAGIC, 2, 0, 0))
+    with gl.GGUFReader(p) as r:
+        assert r.header.version == 2 and not r.tensors
+
+
+def test_unknown_metadata_type(tmp_path):
+    p = tmp_path / "m.gguf"
+    p.write_bytes(struct.pack("<IIQQ", gl.GGUF_MAGIC, 3, 0, 1) + struct.pack("<Q", 1) + b"k" + struct.pack("<I", 13))
+    with pytest.raises(ValueError, match="Unknown metadata value type"):
+        with gl.GGUFReader(p):
+            pass
+
+
+def test_unsupported_tensor_type(tmp_path):
+    p = tmp_path / "q5.gguf"
+    synth.write_gguf(p, [synth.TensorSpec("w", (64,), gl.GGML_TYPE_F32)], contents={"w": np.zeros(64, np.float32)})
+    raw = bytearray(p.read_bytes())
+    i = raw.index(b"w" + struct.pack("<I", 1))           # name, n_dims
+    struct.pack_into("<I", raw, i + 1 + 4 + 8, gl.GGML_TYPE_Q5_0)
+    p.write_bytes(bytes(raw))
+    with gl.GGUFReader(p) as r:
+        assert r.tensors["w"].dtype_name == "Q5_0"
+        with pytest.raises(ValueError, match="Unknown dtype 6"):
+            r.tensors["w"].nbytes
+        with pytest.raises(ValueError, match="Unknown dtype 6"):
+            r.read_tensor("w")
+    assert gl.GGUFTensorInfo("x", 1, (4,), 99, 0).dtype_name == "UNKNOWN(99)"
+
+
+def test_inspect_and_print(golden_dir, capsys):
+    exp = _expected(golden_dir)
+    path = os.path.join(golden_dir, "mini.gguf")
+    info = pfhe_b200.inspect_gguf(path)
+    assert info["version"] == 3 and info["n_tensors"] == 7
+    assert info["tensors"]["blk.0.half.weight"] == {"shape": (3, 5, 32), "dtype": "F16", "numel": 480, "nbytes": 960}
+    assert info["metadata"]["tokenizer.ggml.tokens"] == exp["metadata"]["tokenizer.ggml.tokens"]
+    pfhe_b200.print_gguf_info(path)
+    out = capsys.readouterr().out
+    assert "Tensors: 7" in out and "general.architecture: llama" in out and "token_embd.weight: (48, 64) (Q8_0" in out
+
+
+def test_api_surface_and_defaults():
+    import inspect
+    sig = inspect.signature
+    assert list(sig(gl.GGUFReader.read_tensor).parameters)[:4] == ["self", "name", "device", "dtype"]
+    assert sig(gl.GGUFReader.read_tensor).parameters["device"].default == "cpu"
+    assert sig(gl.GGUFReader.read_tensor).parameters["dtype"].default is torch.float32
+    p = sig(gl.streaming_dequant_context).parameters
+    assert (p["batch_size"].default, p["device"].default, p["dtype"].default) == (4, "cuda", torch.float16)
+    p = sig(gl.GGUFModelPatcher.patch_context).parameters
+    assert (p["device"].default, p["dtype"].default, p["strict"].default) == ("cuda", torch.float16, False)
+    p = sig(gl.tensor_loading_context).parameters
+    assert (p["device"].default, p["dtype"].default) == ("cpu", torch.float32)
+    assert gl.QUANT_INFO == {0: (1, 4), 1: (1, 2), 30: (1, 2), 2: (32, 18), 3: (32, 20), 8: (32, 34)}
+    for name in pfhe_b200.__all__:
+        assert hasattr(pfhe_b200, name)
+
+
+def test_name_mapping():
+    p = gl.GGUFModelPatcher("x.gguf", {"a": "b"})
+    assert p._map_name("a") == "b" and p._map_name("model.layers.0.w") == "layers.0.w" and p._map_name("blk.0") == "blk.0"
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_decode_without_gpu_fails_loudly(golden_dir):
+    with pfhe_b200.tensor_loading_context(os.path.join(golden_dir, "mini.gguf")) as r:
+        with pytest.raises(RuntimeError, match="no CPU fallback"):
+            r.read_tensor("token_embd.weight")
+
+
+def test_llama_specs_match_stated_sizes():
+    s7 = synth.llama_specs(synth.LLAMA2_7B)
+    assert len(s7) == 291
+    q4 = [s for s in s7 if s.ggml_type == gl.GGML_TYPE_Q4_0]
+    assert len(q4) == 224 and sum(s.numel for s in q4) == 6476005376 and sum(s.nbytes for s in q4) == 3642753024
+    s70 = synth.llama_specs(synth.LLAMA3_70B)
+    assert len(s70) == 723
+    q41 = [s for s in s70 if s.ggml_type == gl.GGML_TYPE_Q4_1]
+    assert len(q41) == 560 and sum(s.numel for s in q41) == 68451041280 and sum(s.nbytes for s in q41) == 42781900800
+    q8 = [s for s in s70 if s.ggml_type == gl.GGML_TYPE_Q8_0]
+    assert sum(s.nbytes for s in q8) == 2232680448
+
+
+def test_writer_roundtrip_large_metadata(tmp_path):
+    p = tmp_path / "v.gguf"
+    toks = [f"tok{i}" for i in range(5000)]
+    synth.write_gguf(p, synth.llama_specs(synth.LlamaShape("t", 1, 64, 2, 1, 32, 96, 128, gl.GGML_TYPE_Q4_1)),
+                     [("tokenizer.ggml.tokens", "arr:str", toks), ("tokenizer.ggml.scores", "arr:f32", [0.5] * 5000)])
+    with gl.GGUFReader(p) as r:
+        assert r.metadata["tokenizer.ggml.tokens"] == toks
+        assert r.metadata["tokenizer.ggml.scores"] == [0.5] * 5000
+        last = list(r.tensors.values())[-1]
+        assert r.header.tensor_data_offset + last.offset + last.nbytes == os.path.getsize(p)
+        assert all(t.offset % 32 == 0 for t in r.tensors.values())

@@ -1,0 +1,168 @@
+"""GPU tests of the drop-in Python API: files in, device tensors out, bits as the reference's."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import pfhe_b200
+from conftest import assert_same_bits
+from gpu_util import to_bits
+from oracle import np_oracle
+from pfhe_b200 import gguf_loader as gl
+from pfhe_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def test_mini_file_matches_reference_read_tensor(golden_dir):
+    tens = np.load(os.path.join(golden_dir, "mini_tensors.npz"))
+    with pfhe_b200.tensor_loading_context(os.path.join(golden_dir, "mini.gguf")) as r:
+        for name, info in r.tensors.items():
+            for k, dt in DT.items():
+                for device in ("cuda", "cpu"):
+                    t = r.read_tensor(name, device=device, dtype=dt)
+                    assert t.device.type == device and t.dtype == dt and tuple(t.shape) == info.shape
+                    assert t.is_contiguous()
+                    assert_same_bits(to_bits(t), tens[f"{name}|{k}"], k, f"{name}->{k} on {device}")
+
+
+def test_default_arguments_return_cpu_fp32(golden_dir):
+    tens = np.load(os.path.join(golden_dir, "mini_tensors.npz"))
+    with pfhe_b200.tensor_loading_context(os.path.join(golden_dir, "mini.gguf")) as r:
+        t = r.read_tensor("blk.0.attn_q.weight")
+        assert t.device.type == "cpu" and t.dtype == torch.float32
+        assert_same_bits(to_bits(t), tens["blk.0.attn_q.weight|f32"], "f32")
+        t64 = r.read_tensor("blk.0.attn_q.weight", device="cuda", dtype=torch.float64)
+        assert t64.dtype == torch.float64 and torch.equal(t64.cpu().float(), t)
+        names = [n for n, _ in r.tensor_iterator(pattern="blk.0.*", device="cuda", dtype=torch.float16)]
+        assert names == ["blk.0.attn_norm.weight", "blk.0.attn_q.weight", "blk.0.ffn_up.weight", "blk.0.half.weight"]
+
+
+@pytest.fixture(scope="module")
+def small_llama(tmp_path_factory):
+    shape = synth.LlamaShape("tiny", 2, 256, 4, 2, 64, 704, 512, gl.GGML_TYPE_Q4_0)
+    path = tmp_path_factory.mktemp("gguf") / "tiny.gguf"
+    synth.write_llama_gguf(path, shape, seed=3)
+    return path, shape
+
+
+def _oracle_tensor(reader, name, dtype_key, via=None):
+    info = reader.tensors[name]
+    return np_oracle.read_tensor(info.dtype, reader.read_tensor_raw(name), info.numel, dtype_key, via_dtype=via)
+
+
+def test_streaming_batches(small_llama):
+    path, _ = small_llama
+    with pfhe_b200.streaming_dequant_context(path, batch_size=8, device="cuda", dtype=torch.float16) as stream:
+        names = stream.tensor_names
+        assert len(names) == 2 * 9 + 3
+        seen, kept = [], []
+        for batch in stream.iter_batches():
+            assert 1 <= len(batch) <= 8
+            seen += list(batch)
+            kept.append(batch)                        # earlier batches must stay valid
+        assert seen == names
+        with gl.GGUFReader(path) as r:
+            for batch in kept:
+                for n, t in batch.items():
+                    assert t.is_cuda and t.dtype == torch.float16 and tuple(t.shape) == r.tensors[n].shape
+                    assert_same_bits(to_bits(t), _oracle_tensor(r, n, "f16"), "f16", n)
+        assert [n for n, _ in stream.iter_tensors()] == names
+
+
+def test_tensor_larger_than_a_staging_slot(tmp_path, monkeypatch):
+    """Chunked submits: slot size far below the tensor size, Q4_1 and F32 and a ragged Q8_0."""
+    monkeypatch.setattr(gl._Stager, "slot_bytes", 1 << 16)
+    monkeypatch.setattr(gl._Stager, "n_slots", 3)
+    monkeypatch.setattr(gl._Stager, "_by_device", {})
+    path = tmp_path / "chunky.gguf"
+    specs = [synth.TensorSpec("a", (300, 1024), gl.GGML_TYPE_Q4_1), synth.TensorSpec("b", (100, 777), gl.GGML_TYPE_F32),
+             synth.TensorSpec("c", (200001,), gl.GGML_TYPE_Q8_0), synth.TensorSpec("d", (64, 2048), gl.GGML_TYPE_BF16)]
+    synth.write_gguf(path, specs, seed=9)
+    with gl.GGUFReader(path) as r:
+        for n in r.tensors:
+            for k, dt in DT.items():
+                assert_same_bits(to_bits(r.read_tensor(n, device="cuda", dtype=dt)), _oracle_tensor(r, n, k), k, f"{n}->{k}")
+    st = gl._Stager.get(torch.cuda.current_device())
+    st.wait()
+    assert st.stats()["chunks"] > st.stats()["tensors"]
+    gl._Stager.shutdown()
+
+
+def test_row_shards_tile_the_tensor(small_llama):
+    path, _ = small_llama
+    with gl.GGUFReader(path) as r:
+        name = "blk.1.ffn_up.weight"
+        whole = r.read_tensor(name, device="cuda", dtype=torch.bfloat16)
+        parts = [r.read_tensor(name, device="cuda", dtype=torch.bfloat16, rows=(a, b)) for a, b in ((0, 100), (100, 101), (101, 704))]
+        assert torch.equal(torch.cat(parts).view(torch.int16), whole.view(torch.int16))
+        with pytest.raises(ValueError):
+            r.read_tensor(name, device="cuda", rows=(0, 705))
+
+
+class _Tiny(torch.nn.Module):
+    def __init__(self, shape, dtype, device, rows_div=1):
+        super().__init__()
+        P = lambda *s: torch.nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
+        self.token_embd = torch.nn.Module()
+        self.token_embd.weight = P(shape.vocab // rows_div, shape.hidden)
+        self.output_norm = torch.nn.Module()
+        self.output_norm.weight = P(shape.hidden)
+        self.extra = torch.nn.Module()
+        self.extra.weight = P(3)
+        self.mismatch = torch.nn.Module()
+        self.mismatch.weight = P(5, 5)
+
+
+@pytest.mark.parametrize("param_dtype,load_dtype", [(torch.float16, torch.float16), (torch.float32, torch.float16),
+                                                    (torch.bfloat16, torch.float16), (torch.float16, torch.bfloat16)])
+@pytest.mark.parametrize("device", ["cuda", "cpu"])
+def test_patch_context(small_llama, param_dtype, load_dtype, device):
+    path, shape = small_llama
+    model = _Tiny(shape, param_dtype, device)
+    patcher = pfhe_b200.GGUFModelPatcher(path, {"blk.0.attn_q.weight": "mismatch.weight"})
+    with patcher.patch_context(model, device="cuda", dtype=load_dtype) as stats:
+        assert stats["loaded"] == 2 and stats["skipped"] == len(synth.llama_specs(shape, 2)) - 2
+        assert stats["missing"] == ["extra.weight"] and "blk.0.attn_q.weight" not in stats["unexpected"]
+        key = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}
+        with gl.GGUFReader(path) as r:
+            for gname, p in (("token_embd.weight", model.token_embd.weight), ("output_norm.weight", model.output_norm.weight)):
+                want = _oracle_tensor(r, gname, key[param_dtype], via=key[load_dtype])
+                assert_same_bits(to_bits(p.data), want, key[param_dtype], gname)
+        assert float(model.mismatch.weight.abs().sum()) == 0.0
+    with pytest.raises(ValueError, match="Missing parameters in GGUF"):
+        with patcher.patch_context(model, strict=True):
+            pass
+
+
+def test_patch_context_row_shard(small_llama):
+    path, shape = small_llama
+    with gl.GGUFReader(path) as r:
+        whole = r.read_tensor("token_embd.weight", device="cuda", dtype=torch.bfloat16)
+    for rank in range(4):
+        model = _Tiny(shape, torch.bfloat16, "cuda", rows_div=4)
+        with pfhe_b200.GGUFModelPatcher(path).patch_context(model, dtype=torch.bfloat16, shard=(rank, 4)) as stats:
+            assert stats["loaded"] == 2
+        n = shape.vocab // 4
+        assert torch.equal(model.token_embd.weight.data.view(torch.int16), whole[rank * n:(rank + 1) * n].view(torch.int16))
+
+
+def test_load_gguf_tensors(golden_dir):
+    tens = np.load(os.path.join(golden_dir, "mini_tensors.npz"))
+    out = pfhe_b200.load_gguf_tensors(os.path.join(golden_dir, "mini.gguf"), device="cuda", dtype=torch.bfloat16)
+    assert list(out) == ["token_embd.weight", "blk.0.attn_norm.weight", "blk.0.attn_q.weight", "blk.0.ffn_up.weight",
+                         "blk.0.half.weight", "model.blk.0.bf.weight", "ragged.weight"]
+    for n, t in out.items():
+        assert_same_bits(to_bits(t), tens[f"{n}|bf16"], "bf16", n)
+
+
+def test_truncated_file_raises(tmp_path, golden_dir):
+    data = open(os.path.join(golden_dir, "mini.gguf"), "rb").read()
+    p = tmp_path / "cut.gguf"
+    p.write_bytes(data[:-40])
+    with gl.GGUFReader(p) as r:
+        with pytest.raises(ValueError, match="Data too short"):
+            r.read_tensor("ragged.weight", device="cuda")

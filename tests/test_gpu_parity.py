@@ -1,0 +1,178 @@
+"""GPU parity: every kernel variant against the reference's golden vectors and the CPU oracle.
+
+All calls go through the C ABI (pfhe_dequant_launch*), on device memory owned by torch.
+Integer/bit work: the bar is bit-exact (NaN must meet NaN).
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import CAST2, FORMATS, OUT_DTYPES, assert_same_bits, load_golden
+from gpu_util import decode_on_gpu, to_bits
+from oracle import c_oracle, np_oracle
+from pfhe_b200 import _native, synth
+
+pytestmark = pytest.mark.gpu
+
+QUANT = ("Q4_0", "Q4_1", "Q8_0")
+VARIANTS = {
+    "default": None,
+    "staged": {"variant": 1},
+    "staged_small_tiles": {"variant": 1, "tile_blocks": 8, "stages": 2, "threads": 64, "ctas_per_sm": 1},
+    "staged_deep": {"variant": 1, "tile_blocks": 1024, "stages": 8, "threads": 512, "ctas_per_sm": 1, "streaming_stores": 0},
+    "direct": {"variant": 2},
+    "staged_out": {"variant": 3, "tile_blocks": 128, "stages": 3},
+    "per_element": {"variant": 9},
+}
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+@pytest.mark.parametrize("variant", list(VARIANTS))
+def test_golden_vectors(fmt, dtype, variant):
+    g = load_golden(fmt)
+    got = decode_on_gpu(FORMATS[fmt], g["raw"], int(g["numel"]), dtype, cfg=VARIANTS[variant])
+    assert_same_bits(to_bits(got), g[dtype], dtype, f"{fmt}->{dtype} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("mid,fin", CAST2)
+@pytest.mark.parametrize("variant", ["default", "direct", "staged_out", "per_element"])
+def test_two_step_rounding(fmt, mid, fin, variant):
+    g = load_golden(fmt)
+    got = decode_on_gpu(FORMATS[fmt], g["raw"], int(g["numel"]), fin, mid=mid, cfg=VARIANTS[variant])
+    assert_same_bits(to_bits(got), g[f"{mid}_then_{fin}"], fin, f"{fmt}->{mid}->{fin} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", QUANT)
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+def test_every_finite_scale_bit_pattern(fmt, dtype):
+    """All 63,488 finite fp16 scales, random quants: the fp16 shortcut kernels must round like fp32->fp16."""
+    t = FORMATS[fmt]
+    rng = np.random.default_rng(11)
+    h = np.arange(1 << 16, dtype=np.uint32)
+    h = h[(h & 0x7C00) != 0x7C00].astype(np.uint16)
+    n_blocks = h.size
+    bb = synth.QUANT_INFO[t][1]
+    blocks = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+    blocks[:, 0:2] = h.view(np.uint8).reshape(-1, 2)
+    if fmt == "Q4_1":
+        m = rng.permutation(h)
+        blocks[:, 2:4] = m.view(np.uint8).reshape(-1, 2)
+    raw = blocks.reshape(-1)
+    numel = n_blocks * 32
+    want = c_oracle.read_tensor(t, raw, numel, dtype, n_threads=4)
+    for variant in ("default", "direct", "staged_out"):
+        got = decode_on_gpu(t, raw, numel, dtype, cfg=VARIANTS[variant])
+        assert_same_bits(to_bits(got), want, dtype, f"{fmt}->{dtype} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("numel", [1, 7, 31, 32, 33, 255, 256, 257, 8 * 32 - 1, 8 * 32 + 1, 4096 + 8, 100003])
+def test_ragged_and_tiny_sizes(fmt, numel):
+    t = FORMATS[fmt]
+    raw = synth.random_packed(t, numel, np.random.default_rng(numel))
+    for dtype in OUT_DTYPES:
+        want = np_oracle.read_tensor(t, raw, numel, dtype)
+        for variant in ("default", "direct", "staged_out", "staged_small_tiles"):
+            got = decode_on_gpu(t, raw, numel, dtype, cfg=VARIANTS[variant])
+            assert_same_bits(to_bits(got), want, dtype, f"{fmt} n={numel}->{dtype} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("skew", [2, 4, 6, 10, 14, 1, 3, 7])
+def test_unaligned_source(fmt, skew):
+    """Packed bytes at every kind of offset from a 16-byte line, odd ones included."""
+    t = FORMATS[fmt]
+    numel = 32 * 1031 + 9
+    raw = synth.random_packed(t, numel, np.random.default_rng(skew))
+    for dtype in ("f16", "f32"):
+        want = np_oracle.read_tensor(t, raw, numel, dtype)
+        for variant in ("default", "staged_out", "staged_small_tiles"):
+            got = decode_on_gpu(t, raw, numel, dtype, skew=skew, cfg=VARIANTS[variant])
+            assert_same_bits(to_bits(got), want, dtype, f"{fmt} skew={skew}->{dtype} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+def test_unaligned_destination(fmt, dtype):
+    t = FORMATS[fmt]
+    numel = 32 * 300 + 3
+    raw = synth.random_packed(t, numel, np.random.default_rng(3))
+    want = np_oracle.read_tensor(t, raw, numel, dtype)
+    for off in (1, 3):
+        got = decode_on_gpu(t, raw, numel, dtype, dst_skew_elems=off)
+        assert_same_bits(to_bits(got), want, dtype, f"{fmt}->{dtype} dst+{off}")
+
+
+def test_empty_tensor_and_errors():
+    L = _native.lib()
+    src = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(64, dtype=torch.float16, device="cuda")
+    assert L.pfhe_dequant_launch(2, 1, src.data_ptr(), 0, dst.data_ptr(), 0, 0, None) == 0
+    assert L.pfhe_dequant_launch(2, 1, src.data_ptr(), 17, dst.data_ptr(), 128, 32, None) == _native.ERR_SHORT_SOURCE
+    assert L.pfhe_dequant_launch(2, 1, src.data_ptr(), 18, dst.data_ptr(), 62, 32, None) == _native.ERR_SHORT_DEST
+    assert L.pfhe_dequant_launch(9, 1, src.data_ptr(), 64, dst.data_ptr(), 128, 32, None) == _native.ERR_BAD_TYPE
+    assert L.pfhe_dequant_launch(2, 5, src.data_ptr(), 64, dst.data_ptr(), 128, 32, None) == _native.ERR_BAD_DTYPE
+    assert L.pfhe_dequant_launch(2, 1, None, 18, dst.data_ptr(), 128, 32, None) == _native.ERR_BAD_ARG
+    torch.cuda.synchronize()
+    assert (dst == 0).all()
+
+
+# --- the benchmark configurations at full size -------------------------------------------------
+def _config_tensor(fmt, shape, seed):
+    numel = shape[0] * shape[1]
+    raw = synth.random_packed(FORMATS[fmt], numel, np.random.default_rng(seed))
+    return raw, numel
+
+
+def test_config1_q8_0_4096x4096_to_f32():
+    raw, numel = _config_tensor("Q8_0", (4096, 4096), 1)
+    assert raw.size == 17825792
+    want = c_oracle.read_tensor(FORMATS["Q8_0"], raw, numel, "f32", n_threads=8)
+    got = decode_on_gpu(FORMATS["Q8_0"], raw, numel, "f32")
+    assert_same_bits(to_bits(got), want, "f32", "config 1")
+
+
+@pytest.mark.parametrize("fmt,nbytes", [("Q4_0", 25362432), ("Q4_1", 28180480)])
+def test_config2_11008x4096_to_f16(fmt, nbytes):
+    raw, numel = _config_tensor(fmt, (11008, 4096), 2)
+    assert raw.size == nbytes
+    want = c_oracle.read_tensor(FORMATS[fmt], raw, numel, "f16", n_threads=8)
+    for variant in ("default", "direct", "staged_out"):
+        got = decode_on_gpu(FORMATS[fmt], raw, numel, "f16", cfg=VARIANTS[variant])
+        assert_same_bits(to_bits(got), want, "f16", f"config 2 {fmt} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_large_tensor_properties(fmt, dtype):
+    """At sweep sizes the oracle is too slow to run in full, so use structure:
+    a tensor made of one 1 MiB-element tile repeated must decode to the oracle's
+    tile repeated (every CTA, stage and tail position sees known data), and
+    decoding the two halves separately must equal decoding the whole."""
+    t = FORMATS[fmt]
+    tile_elems = 1 << 20
+    reps = 96 if fmt in QUANT else 48
+    tile = synth.random_packed(t, tile_elems, np.random.default_rng(17))
+    raw = np.tile(tile, reps)
+    numel = tile_elems * reps
+    want_tile = torch.from_numpy(c_oracle.read_tensor(t, tile, tile_elems, dtype, n_threads=8).view(np.int16)).cuda()
+    got = decode_on_gpu(t, raw, numel, dtype)
+    g = got.view(torch.int16).view(reps, tile_elems)
+    assert bool((g == want_tile.unsqueeze(0)).all())
+    half = numel // 2
+    hb = raw.size // 2
+    a = decode_on_gpu(t, raw[:hb], half, dtype)
+    b = decode_on_gpu(t, raw[hb:], half, dtype)
+    assert torch.equal(torch.cat([a, b]).view(torch.int16), got.view(torch.int16))
+
+
+def test_decode_is_idempotent_and_launches_are_counted():
+    L = _native.lib()
+    raw, numel = _config_tensor("Q4_1", (1024, 4096), 4)
+    before = L.pfhe_launch_count()
+    a = decode_on_gpu(FORMATS["Q4_1"], raw, numel, "bf16")
+    b = decode_on_gpu(FORMATS["Q4_1"], raw, numel, "bf16")
+    assert L.pfhe_launch_count() == before + 2
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))

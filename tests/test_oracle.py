@@ -1,0 +1,89 @@
+"""Pins the three CPU restatements under oracle/ to vectors made by running the reference."""
+import numpy as np
+import pytest
+
+from conftest import CAST2, FORMATS, OUT_DTYPES, assert_same_bits, load_golden
+from oracle import c_oracle, loop_port, np_oracle
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+def test_numpy_oracle_matches_reference(fmt, dtype):
+    g = load_golden(fmt)
+    got = np_oracle.read_tensor(FORMATS[fmt], g["raw"], int(g["numel"]), dtype)
+    assert_same_bits(got, g[dtype], dtype, f"{fmt}->{dtype}")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+@pytest.mark.parametrize("threads", [1, 3])
+def test_c_oracle_matches_reference(fmt, dtype, threads):
+    g = load_golden(fmt)
+    got = c_oracle.read_tensor(FORMATS[fmt], g["raw"], int(g["numel"]), dtype, n_threads=threads)
+    assert_same_bits(got, g[dtype], dtype, f"{fmt}->{dtype}")
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+@pytest.mark.parametrize("mid,fin", CAST2)
+def test_two_step_rounding_matches_reference(fmt, mid, fin):
+    g = load_golden(fmt)
+    want = g[f"{mid}_then_{fin}"]
+    assert_same_bits(np_oracle.read_tensor(FORMATS[fmt], g["raw"], int(g["numel"]), fin, via_dtype=mid), want, fin)
+    assert_same_bits(c_oracle.read_tensor(FORMATS[fmt], g["raw"], int(g["numel"]), fin, via_dtype=mid), want, fin)
+
+
+@pytest.mark.parametrize("fmt", ["Q4_0", "Q4_1", "Q8_0"])
+def test_loop_port_matches_reference(fmt):
+    g = load_golden(fmt)
+    got = loop_port.read_tensor_loop(FORMATS[fmt], g["raw"].tobytes(), int(g["numel"]), "f16")
+    assert_same_bits(got, g["f16"], "f16", fmt)
+
+
+def test_nibble_order_is_interleaved():
+    # byte j -> outputs 2j (low nibble) and 2j+1 (high nibble), not ggml's split halves
+    blk = np.zeros(18, dtype=np.uint8)
+    blk[0:2] = np.array([1.0], dtype=np.float16).view(np.uint8)
+    blk[2] = 0x1F            # low nibble 15, high nibble 1
+    out = np_oracle.decode_f32(FORMATS["Q4_0"], blk, 32)
+    assert out[0] == 7.0 and out[1] == -7.0 and out[2] == -8.0
+
+
+def test_negative_scale_times_zero_is_negative_zero():
+    blk = np.full(18, 0x88, dtype=np.uint8)
+    blk[0:2] = np.array([-2.0], dtype=np.float16).view(np.uint8)
+    for impl in (np_oracle.read_tensor, c_oracle.read_tensor):
+        out = impl(FORMATS["Q4_0"], blk, 32, "f32")
+        assert np.all(out.view(np.uint32) == 0x80000000)
+
+
+def test_short_source_raises_value_error():
+    for impl in (np_oracle.read_tensor, c_oracle.read_tensor):
+        with pytest.raises(ValueError, match="Data too short"):
+            impl(FORMATS["Q4_0"], np.zeros(17, dtype=np.uint8), 32, "f32")
+
+
+def test_unknown_type():
+    with pytest.raises(ValueError):
+        np_oracle.nbytes(12, 256)
+    with pytest.raises(NotImplementedError):
+        c_oracle.read_tensor(12, np.zeros(256, dtype=np.uint8), 32)
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+def test_oracles_agree_on_seeded_blocks(fmt):
+    """Wider sweep than the golden files: all finite fp16 scale bit patterns appear."""
+    from pfhe_b200 import synth
+    rng = np.random.default_rng(5)
+    t = FORMATS[fmt]
+    numel = 32 * 4096
+    raw = synth.random_packed(t, numel, rng).copy()
+    if fmt in ("Q4_0", "Q4_1", "Q8_0"):
+        bb = synth.QUANT_INFO[t][1]
+        blocks = raw.reshape(-1, bb)
+        h = np.arange(4096, dtype=np.uint32) * 16 + rng.integers(0, 16, 4096)
+        h = np.where((h & 0x7C00) == 0x7C00, h & 0xBFFF, h).astype(np.uint16)
+        blocks[:, 0:2] = h.view(np.uint8).reshape(-1, 2)
+    for dtype in OUT_DTYPES:
+        a = np_oracle.read_tensor(t, raw, numel, dtype)
+        b = c_oracle.read_tensor(t, raw, numel, dtype, n_threads=2)
+        assert_same_bits(b, a, dtype, f"{fmt}->{dtype}")
