@@ -1,0 +1,448 @@
+"""Benchmark of the GGUF block-decode hot path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU port of the reference's decode
+
+A step is one pass of the hot path over one batch of synthetic tensors: the
+Q4_0 11008x4096 -> fp16 tensor of the second benchmark configuration, BATCH
+distinct copies of it so that the working set (BATCH x 115.5 MB) is far larger
+than the 126 MB L2.  ``value`` is decoded output GB/s with the packed bytes
+already in HBM; ``e2e`` is the same metric through ``GGUFReader.read_tensor``
+from a GGUF file on the host (mmap -> pinned ring -> H2D -> decode), with a
+small device->host read of each step's result inside the timed region.  With
+N > 1 (torchrun) every rank decodes its own batch -- tensors are independent,
+there is no data-path collective -- and the value is the sum over ranks divided
+by the slowest rank's device time.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+Q4_0, Q4_1, Q8_0 = 2, 3, 8
+ROWS, COLS = 11008, 4096
+NUMEL = ROWS * COLS
+METRIC = "dequant_output_gbps_q4_0_11008x4096_to_fp16"
+UNIT = "GB/s"
+WORKLOAD = "config2: Q4_0 11008x4096 -> fp16 (Llama-7B FFN shape), seeded synthetic blocks"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, device copy read+write)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU legs (the oracle is used here as the timed baseline only)
+# ---------------------------------------------------------------------------------------------
+def cpu_sample_rows(budget_s: float) -> int:
+    """Rows of the 11008x4096 tensor the per-block Python loop decodes in about budget_s."""
+    from oracle import loop_port
+    from pfhe_b200 import synth
+    probe_rows = 8
+    raw = synth.random_packed(Q4_0, probe_rows * COLS, np.random.default_rng(0)).tobytes()
+    t0 = time.perf_counter()
+    loop_port.read_tensor_loop(Q4_0, raw, probe_rows * COLS, "f16")
+    per_row = (time.perf_counter() - t0) / probe_rows
+    return int(max(16, min(ROWS, budget_s / per_row)))
+
+
+def cpu_loop_step(raw_bytes: bytes, rows: int) -> float:
+    from oracle import loop_port
+    t0 = time.perf_counter()
+    out = loop_port.read_tensor_loop(Q4_0, raw_bytes, rows * COLS, "f16")
+    dt = time.perf_counter() - t0
+    assert out.size == rows * COLS
+    return dt
+
+
+def cpu_extras(raw: np.ndarray) -> dict:
+    """Stronger CPU implementations of the same arithmetic, for context."""
+    import torch
+    from oracle import c_oracle
+    extras = {}
+    threads = c_oracle.max_threads()
+    out = np.empty(NUMEL, dtype=np.float16)
+    scratch = np.empty(NUMEL, dtype=np.float32)
+    c_oracle.read_tensor(Q4_0, raw, NUMEL, "f16", n_threads=threads, out=out, scratch=scratch)
+    t0 = time.perf_counter()
+    c_oracle.read_tensor(Q4_0, raw, NUMEL, "f16", n_threads=threads, out=out, scratch=scratch)
+    extras["c_openmp"] = {"value": NUMEL * 2 / (time.perf_counter() - t0) / 1e9, "unit": UNIT, "cores": threads,
+                          "sample": "one full 11008x4096 tensor"}
+    # torch-op formulation (the reference's gguf_cuda.py:83-116 restated) on the host cores
+    def torch_q4_0(rawt):
+        blk = rawt.view(-1, 18)
+        d = blk[:, :2].contiguous().view(torch.float16).to(torch.float32)
+        qs = blk[:, 2:]
+        lo = (qs & 0x0F).to(torch.int16) - 8
+        hi = (qs >> 4).to(torch.int16) - 8
+        return (torch.stack([lo, hi], dim=2).view(-1, 32).to(torch.float32) * d).view(-1).to(torch.float16)
+    rawt = torch.from_numpy(raw)
+    torch_q4_0(rawt)
+    t0 = time.perf_counter()
+    torch_q4_0(rawt)
+    extras["torch_ops"] = {"value": NUMEL * 2 / (time.perf_counter() - t0) / 1e9, "unit": UNIT,
+                           "cores": torch.get_num_threads(), "sample": "one full 11008x4096 tensor"}
+    return extras
+
+
+def run_reference_arm(args) -> None:
+    """Times the CPU port of the reference's per-block decode loop on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from pfhe_b200 import synth
+    total_steps = args.steps + args.warmup
+    rows = cpu_sample_rows(min(4.0, 150.0 / max(total_steps, 1)))
+    raw = synth.random_packed(Q4_0, rows * COLS, np.random.default_rng(2)).tobytes()
+    for _ in range(args.warmup):
+        cpu_loop_step(raw, rows)
+    times = [cpu_loop_step(raw, rows) for _ in range(args.steps)]
+    dt = float(np.mean(times))
+    value = rows * COLS * 2 / dt / 1e9
+    sample = f"{rows} of {ROWS} rows of one tensor per step ({rows * COLS // 32} blocks), single thread"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 arithmetic, f16 out", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample,
+                   "note": "the reference is pure Python and is not installed on this machine; this is the "
+                           "oracle's per-block loop port of gguf_loader.py:430-476, which keeps its cost structure"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_gpu_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import pfhe_b200
+    from pfhe_b200 import _native, gguf_loader as gl, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    L = _native.lib()
+    batch = args.batch
+    in_bytes = L.pfhe_tensor_nbytes(Q4_0, NUMEL)
+    out_bytes = NUMEL * 2
+    algo_bytes = in_bytes + out_bytes                      # 0.5625 + 2 bytes per element
+
+    # --- device-resident inputs: BATCH distinct seeded tensors ---------------------------
+    rng = np.random.default_rng([2, rank])
+    host_raw = [synth.random_packed(Q4_0, NUMEL, rng) for _ in range(batch)]
+    srcs = [torch.from_numpy(r).to(dev) for r in host_raw]
+    dsts = [torch.empty((ROWS, COLS), dtype=torch.float16, device=dev) for _ in range(batch)]
+    stream = torch.cuda.current_stream()
+
+    descs = (_native.TensorDesc * batch)()
+    for i, (s, d) in enumerate(zip(srcs, dsts)):
+        descs[i] = _native.TensorDesc(Q4_0, _native.OUT_F16, s.data_ptr(), in_bytes, d.data_ptr(), out_bytes, NUMEL)
+
+    def decode_step():
+        # one step = one batch of tensors = ONE kernel launch (pfhe_dequant_launch_batch)
+        rc = L.pfhe_dequant_launch_batch(descs, batch, stream.cuda_stream)
+        if rc:
+            _native.check(rc)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        decode_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_timed0 = L.pfhe_launch_count()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for a, b in ev:
+        a.record(stream)
+        decode_step()
+        b.record(stream)
+    barrier()
+    total_ms = ev[0][0].elapsed_time(ev[-1][1])
+    gpu_launches = L.pfhe_launch_count() - launches_timed0
+    launches_per_step = gpu_launches // args.steps
+    # duration of the dominant kernel: CUDA events around each launch of the timed region
+    launch_ms = float(np.mean([a.elapsed_time(b) for a, b in ev])) / launches_per_step
+    _native.check(L.pfhe_device_status(local_rank))
+
+    # --- the same tensors one launch each (pfhe_dequant_launch), for comparison ---------------
+    def single_step():
+        for s, d in zip(srcs, dsts):
+            L.pfhe_dequant_launch(Q4_0, _native.OUT_F16, s.data_ptr(), in_bytes, d.data_ptr(), out_bytes, NUMEL, stream.cuda_stream)
+    for _ in range(3):
+        single_step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(max(args.steps // 2, 2)):
+        single_step()
+    b.record(stream)
+    torch.cuda.synchronize()
+    single_launch_ms = a.elapsed_time(b) / (max(args.steps // 2, 2) * batch)
+
+    # --- other formats of the same shape, same method (reported, not the headline) ----------
+    per_format = {}
+    for name, t, odt, oid in (("Q4_1->f16", Q4_1, torch.float16, _native.OUT_F16), ("Q8_0->f16", Q8_0, torch.float16, _native.OUT_F16),
+                              ("Q4_0->bf16", Q4_0, torch.bfloat16, _native.OUT_BF16), ("Q4_1->bf16", Q4_1, torch.bfloat16, _native.OUT_BF16)):
+        nb = L.pfhe_tensor_nbytes(t, NUMEL)
+        fs = [torch.from_numpy(synth.random_packed(t, NUMEL, np.random.default_rng([3, rank, i]))).to(dev) for i in range(4)]
+        fs = [fs[i % 4] if i < 4 else fs[i % 4].clone() for i in range(batch)]
+        fd = [d.view(odt) for d in dsts]
+        def fstep():
+            for s, d in zip(fs, fd):
+                L.pfhe_dequant_launch(t, oid, s.data_ptr(), nb, d.data_ptr(), out_bytes, NUMEL, stream.cuda_stream)
+        for _ in range(3):
+            fstep()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(max(args.steps // 2, 2)):
+            fstep()
+        b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / (max(args.steps // 2, 2) * batch)
+        per_format[name] = {"output_gbps": out_bytes / ms / 1e6, "hbm_gbps": (nb + out_bytes) / ms / 1e6}
+        del fs
+
+    # --- end to end through the public API: GGUF file on the host -> device tensors ----------
+    e2e = run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # --- max over ranks -------------------------------------------------------------------
+    t = torch.tensor([total_ms, e2e["ms_per_step"]], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max, e2e_ms_max = float(t[0]), float(t[1])
+    value = world * args.steps * batch * out_bytes / total_ms_max / 1e6
+    e2e_value = world * batch * out_bytes / e2e_ms_max / 1e6
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        achieved = algo_bytes * batch / launches_per_step / launch_ms / 1e6
+        cpu_base = None
+        if world == 1:
+            rows = cpu_sample_rows(12.0)
+            dt = cpu_loop_step(host_raw[0][: rows * COLS // 32 * 18].tobytes(), rows)
+            cpu_base = {"value": rows * COLS * 2 / dt / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+                        "sample": f"{rows} of {ROWS} rows of one of the step's tensors, per-block Python loop port, single thread",
+                        "also": cpu_extras(host_raw[0])}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 multiply of exact small integers (bit-identical to the reference's f32 path), f16 out",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tensors_per_step": batch, "parallelism": f"independent tensors per GPU x{world}",
+                       "l2": f"inputs larger than L2: {batch} distinct tensors, {batch * algo_bytes / 1e6:.0f} MB touched per step",
+                       "in_bytes_per_tensor": in_bytes, "out_bytes_per_tensor": out_bytes},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": args.traffic_bytes, "peak_kind": peak_kind,
+                         "kernel": "dequant_blocks_batch", "launches_per_step": launches_per_step,
+                         "algorithmic_bytes_per_launch": algo_bytes * batch // launches_per_step, "launch_ms": launch_ms,
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         "one_tensor_per_launch": {"launch_ms": single_launch_ms, "achieved": algo_bytes / single_launch_ms / 1e6,
+                                                   "kernel": "dequant_blocks_staged"}},
+            "per_format": per_format,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                    "api": "GGUFReader.read_tensor(name, device='cuda', dtype=torch.float16) on a GGUF file in " + e2e["where"],
+                    "host_copy_seconds_per_step": e2e["host_copy_s"], "slot_wait_seconds_per_step": e2e["slot_wait_s"]},
+            "gpu_launches": int(gpu_launches),
+            "clocks": clocks,
+        }
+        if cpu_base is not None:
+            line["cpu_baseline"] = cpu_base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch):
+    """Public API, host buffers: every step reads BATCH tensors from a GGUF file."""
+    batch = len(host_raw)
+    base = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tempfile.gettempdir()
+    path = os.path.join(base, f"pfhe_bench_rank{rank}_{os.getpid()}.gguf")
+    specs = [synth.TensorSpec(f"blk.{i}.ffn_up.weight", (ROWS, COLS), Q4_0) for i in range(batch)]
+    synth.write_gguf(path, specs, synth.llama_metadata(synth.LLAMA2_7B, batch),
+                     contents={s.name: r for s, r in zip(specs, host_raw)})
+    try:
+        pinned_probe = torch.empty(64, dtype=torch.float16).pin_memory()
+        stager = gl._Stager.get(dev.index)
+        with pfhe_b200.tensor_loading_context(path) as reader:
+            names = list(reader.tensors)
+
+            def step():
+                last = None
+                for n, d in zip(names, dsts):
+                    last = reader.read_tensor(n, dtype=torch.float16, out=d)
+                pinned_probe.copy_(last.view(-1)[-64:], non_blocking=True)   # device -> host read of the result
+
+            for _ in range(2):
+                step()
+            torch.cuda.synchronize()
+            s0 = stager.stats()
+            n_steps = max(args.steps // 2, 2)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            a.record()
+            for _ in range(n_steps):
+                step()
+            b.record()
+            torch.cuda.synchronize()
+            wall_ms = (time.perf_counter() - t0) * 1e3
+            dev_ms = a.elapsed_time(b)
+            s1 = stager.stats()
+        ms = max(wall_ms, dev_ms) / n_steps
+        return {"ms_per_step": ms, "h2d": sum(s.nbytes for s in specs), "d2h": 128, "where": base,
+                "host_copy_s": (s1["host_copy_seconds"] - s0["host_copy_seconds"]) / n_steps,
+                "slot_wait_s": (s1["slot_wait_seconds"] - s0["slot_wait_seconds"]) / n_steps}
+    finally:
+        try:
+            os.unlink(path)
+        except OSError:
+            pass
+
+
+def run_kernel_case(spec: str) -> None:
+    """A few launches of one decode kernel on device-resident data (the case profilers capture).
+
+    spec = FORMAT:OUT:NUMEL[:LAUNCHES], e.g. Q4_0:f16:134217728:6
+    """
+    import torch
+    from pfhe_b200 import _native, synth
+    parts = spec.split(":")
+    fmt = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8, "F16": 1, "BF16": 30, "F32": 0}[parts[0]]
+    oid, odt = {"f32": (0, torch.float32), "f16": (1, torch.float16), "bf16": (2, torch.bfloat16)}[parts[1]]
+    numel = int(parts[2])
+    launches = int(parts[3]) if len(parts) > 3 else 6
+    L = _native.lib()
+    nb = L.pfhe_tensor_nbytes(fmt, numel)
+    chunk = 1 << 22
+    tile = torch.from_numpy(synth.random_packed(fmt, chunk, np.random.default_rng(1))).cuda()
+    reps = -(-nb // tile.numel())
+    src = tile.repeat(reps)[:nb].contiguous()
+    dsts = [torch.empty(numel, dtype=odt, device="cuda") for _ in range(2)]
+    st = torch.cuda.current_stream()
+    evs = []
+    for i in range(launches):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(st)
+        _native.check(L.pfhe_dequant_launch(fmt, oid, src.data_ptr(), nb, dsts[i & 1].data_ptr(),
+                                            numel * dsts[0].element_size(), numel, st.cuda_stream))
+        b.record(st)
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    ms = sorted(a.elapsed_time(b) for a, b in evs[1:])[len(evs[1:]) // 2]
+    total = nb + numel * dsts[0].element_size()
+    print(json.dumps({"kernel_case": spec, "in_bytes": nb, "out_bytes": numel * dsts[0].element_size(),
+                      "median_ms": ms, "hbm_gbps": total / ms / 1e6}), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--batch", type=int, default=16, help="tensors per step")
+    ap.add_argument("--traffic-bytes", type=float, default=None,
+                    help="DRAM bytes per launch from an ncu capture (profiles/), echoed into the roofline object")
+    ap.add_argument("--kernel-case", default=None,
+                    help="FORMAT:OUT:NUMEL[:LAUNCHES] -- run only a few launches of one kernel (for profilers)")
+    args = ap.parse_args()
+    if args.kernel_case:
+        run_kernel_case(args.kernel_case)
+    elif args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

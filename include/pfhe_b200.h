@@ -102,7 +102,9 @@ typedef struct pfhe_launch_cfg {
     int32_t threads;      /* threads per CTA (multiple of 32) */
     int32_t ctas_per_sm;  /* grid = SM count * ctas_per_sm */
     int32_t streaming_stores; /* 1: evict-first stores; 0: default; -1: library default */
-    int32_t reserved[2];
+    int32_t reserved[2];  /* [0]: 0/2 = tiles dealt round-robin to the CTAs (default), 1 = one contiguous run per CTA;
+                             [1]: 0 = tile_blocks is a target, adjusted so the tiles fill whole rounds of the grid,
+                                  1 = use tile_blocks exactly */
 } pfhe_launch_cfg;
 
 int pfhe_dequant_launch_ex(int ggml_type, int mid_dtype, int out_dtype,
@@ -110,6 +112,32 @@ int pfhe_dequant_launch_ex(int ggml_type, int mid_dtype, int out_dtype,
                            void *dst_dev, int64_t dst_bytes,
                            int64_t n_elements, void *stream,
                            const pfhe_launch_cfg *cfg);
+
+/* One tensor of a batch: the arguments of pfhe_dequant_launch as a record. */
+typedef struct pfhe_tensor_desc {
+    int32_t ggml_type;
+    int32_t out_dtype;
+    const void *src_dev;
+    int64_t src_bytes;
+    void *dst_dev;
+    int64_t dst_bytes;
+    int64_t n_elements;
+} pfhe_tensor_desc;
+
+/*
+ * Decode n_tensors device-resident tensors in as few launches as possible.
+ * Replaces the per-tensor loop of StreamingDequantizer.iter_batches
+ * (gguf_loader.py:637-650) for packed bytes that are already in device memory:
+ * quantised tensors (2-byte aligned source, 16-byte aligned destination) share
+ * one kernel launch per 32 tensors, every other tensor gets its own launch.
+ * Results are identical to n_tensors calls of pfhe_dequant_launch.  All
+ * arguments are checked before anything is launched.
+ */
+int pfhe_dequant_launch_batch(const pfhe_tensor_desc *tensors, int n_tensors, void *stream);
+
+/* As pfhe_dequant_launch_batch with an explicit kernel shape (threads, ctas_per_sm, tile_blocks, stages). */
+int pfhe_dequant_launch_batch_ex(const pfhe_tensor_desc *tensors, int n_tensors, void *stream,
+                                 const pfhe_launch_cfg *cfg);
 
 /*
  * Reads and clears the device-side wait status of `device` (-1 = current).

@@ -22,7 +22,7 @@ OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
 # Every symbol include/pfhe_b200.h declares.
 EXPORTED_SYMBOLS = (
     "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes",
-    "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex",
+    "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex", "pfhe_dequant_launch_batch", "pfhe_dequant_launch_batch_ex",
     "pfhe_device_status", "pfhe_launch_count",
     "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd",
     "pfhe_loader_wait", "pfhe_loader_get_stats", "pfhe_loader_destroy",
@@ -33,6 +33,12 @@ class LaunchCfg(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_int32), ("tile_blocks", ctypes.c_int32), ("stages", ctypes.c_int32),
                 ("threads", ctypes.c_int32), ("ctas_per_sm", ctypes.c_int32), ("streaming_stores", ctypes.c_int32),
                 ("reserved", ctypes.c_int32 * 2)]
+
+
+class TensorDesc(ctypes.Structure):
+    _fields_ = [("ggml_type", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("src_dev", ctypes.c_void_p),
+                ("src_bytes", ctypes.c_int64), ("dst_dev", ctypes.c_void_p), ("dst_bytes", ctypes.c_int64),
+                ("n_elements", ctypes.c_int64)]
 
 
 class LoaderStats(ctypes.Structure):
@@ -65,6 +71,10 @@ def lib() -> ctypes.CDLL:
     L.pfhe_dequant_launch_cast2.argtypes = [i32, i32, i32, vp, i64, vp, i64, i64, vp]
     L.pfhe_dequant_launch_ex.restype = i32
     L.pfhe_dequant_launch_ex.argtypes = [i32, i32, i32, vp, i64, vp, i64, i64, vp, ctypes.POINTER(LaunchCfg)]
+    L.pfhe_dequant_launch_batch.restype = i32
+    L.pfhe_dequant_launch_batch.argtypes = [ctypes.POINTER(TensorDesc), i32, vp]
+    L.pfhe_dequant_launch_batch_ex.restype = i32
+    L.pfhe_dequant_launch_batch_ex.argtypes = [ctypes.POINTER(TensorDesc), i32, vp, ctypes.POINTER(LaunchCfg)]
     L.pfhe_device_status.restype = i32
     L.pfhe_device_status.argtypes = [i32]
     L.pfhe_launch_count.restype = i64

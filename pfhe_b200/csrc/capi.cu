@@ -26,6 +26,7 @@ void set_error(const char *fmt, ...)
 int cuda_fail(cudaError_t e, const char *what)
 {
     set_error("%s: %s", what, cudaGetErrorString(e));
+    (void)cudaGetLastError();   // do not let this failure show up in a later launch check
     return PFHE_ERR_CUDA;
 }
 
@@ -78,13 +79,16 @@ int status_word(int dev, int **out)
     return PFHE_OK;
 }
 
+// Dynamic shared memory a kernel may use next to its static part.
+constexpr size_t kSmemBudget = 227 * 1024 - 1024;
+
 static int ensure_smem(const void *kernel, int dev, size_t bytes)
 {
     if (bytes <= 48 * 1024) return PFHE_OK;
     std::lock_guard<std::mutex> lk(g_mu);
     uint64_t &mask = g_smem_configured[kernel];
     if (mask & (1ull << dev)) return PFHE_OK;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
     mask |= 1ull << dev;
     return PFHE_OK;
@@ -169,6 +173,24 @@ static int check_launch(cudaStream_t stream, const char *what)
     return PFHE_OK;
 }
 
+// Tile length (blocks, multiple of 8) near `target` such that the tiles dealt
+// round-robin to `grid` CTAs fill whole rounds: every CTA gets the same number
+// of tiles, give or take one short tile at the very end.
+static int balanced_tile_blocks(int64_t n_blocks, int64_t grid, int target, int max_tile)
+{
+    const int64_t n_groups = (n_blocks + 7) / 8;
+    const int64_t tg_target = target / 8 > 0 ? target / 8 : 1;
+    int64_t rounds = (n_groups + grid * tg_target / 2) / (grid * tg_target);
+    if (rounds < 1) rounds = 1;
+    int64_t tg = (n_groups + grid * rounds - 1) / (grid * rounds);
+    while (tg * 8 > max_tile) {
+        ++rounds;
+        tg = (n_groups + grid * rounds - 1) / (grid * rounds);
+    }
+    if (tg < 1) tg = 1;
+    return (int)(tg * 8);
+}
+
 // Default shapes, chosen from measurements on B200 (148 SMs).
 static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
 {
@@ -176,9 +198,21 @@ static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
     if (c->variant == 0) c->variant = 1;
     if (c->threads <= 0) c->threads = 256;
     if (c->stages <= 0) c->stages = 4;
-    if (c->ctas_per_sm <= 0) c->ctas_per_sm = 4;
+    if (c->ctas_per_sm <= 0) c->ctas_per_sm = 2;
     if (c->tile_blocks <= 0) c->tile_blocks = (ggml_type == T_Q8_0) ? 256 : 512;
     if (c->streaming_stores < 0) c->streaming_stores = 1;
+}
+
+static void fill_packed(PackedTensor *t, const uint8_t *src, void *dst, int64_t n, int block_bytes)
+{
+    const uintptr_t s = reinterpret_cast<uintptr_t>(src);
+    t->skew = (int)(s & 15);
+    t->src16 = src - t->skew;
+    t->dst = dst;
+    t->n_elements = n;
+    t->n_blocks = (n + 31) / 32;
+    t->span_bytes = (t->skew + t->n_blocks * block_bytes + 15) & ~(int64_t)15;
+    t->kind = 0;
 }
 
 int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_bytes, void *dst, int64_t dst_bytes,
@@ -265,22 +299,29 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     }
 
     BlockKernelArgs a;
-    a.skew = (int)(s & 15);
-    a.src16 = src8 - a.skew;
-    a.dst = dst;
-    a.n_elements = n;
-    a.n_blocks = n_blocks;
-    a.span_bytes = (a.skew + n_blocks * bb + 15) & ~(int64_t)15;
+    fill_packed(&a.t, src8, dst, n, bb);
     a.tile_blocks = cfg.tile_blocks;
     a.stages = cfg.stages;
+    a.interleaved = cfg.reserved[0] == 1 ? 0 : 1;
     if ((rc = status_word(dev, &a.status))) return rc;
 
-    // Small tensors: fewer CTAs and shallower tiles, so every CTA has work.
+    // Small tensors: fewer CTAs, so every CTA has at least one 8-block group.
     const int64_t n_groups = (n_blocks + 7) / 8;
-    int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
-    const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
-    if (groups_per_cta * 8 < a.tile_blocks) a.tile_blocks = (int)(groups_per_cta * 8);
-    const int64_t tiles_per_cta = (groups_per_cta * 8 + a.tile_blocks - 1) / a.tile_blocks;
+    const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
+    if (cfg.reserved[1] == 0) {
+        // Tiles near the requested length that fill whole rounds of the grid.
+        const int out_per_block = variant == 3 ? 2 * 32 * osz : 0;
+        const size_t per_cta = kSmemBudget / (size_t)(cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 1) - 1024;
+        int max_tile = (int)(per_cta / ((size_t)a.stages * bb + out_per_block) - 16) / 8 * 8;
+        if (max_tile > 2048) max_tile = 2048;
+        if (max_tile < 8) max_tile = 8;
+        a.tile_blocks = balanced_tile_blocks(n_blocks, grid, a.tile_blocks, max_tile);
+    } else {
+        const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
+        if (groups_per_cta * 8 < a.tile_blocks) a.tile_blocks = (int)(groups_per_cta * 8);
+    }
+    const int64_t tiles = (n_blocks + a.tile_blocks - 1) / a.tile_blocks;
+    const int64_t tiles_per_cta = (tiles + grid - 1) / grid;
     if (tiles_per_cta < a.stages) a.stages = (int)tiles_per_cta;
 
     size_t smem = (size_t)a.stages * (a.tile_blocks * bb + 16);
@@ -289,10 +330,104 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
         smem = ((smem + 127) & ~(size_t)127) + 2 * (size_t)a.tile_blocks * 32 * osz;
         fn = k.staged_out;
     }
-    if (smem > 227 * 1024) { set_error("tile configuration needs %zu bytes of shared memory", smem); return PFHE_ERR_BAD_ARG; }
+    if (smem > kSmemBudget) { set_error("tile configuration needs %zu bytes of shared memory", smem); return PFHE_ERR_BAD_ARG; }
     if ((rc = ensure_smem(reinterpret_cast<const void *>(fn), dev, smem))) return rc;
     fn<<<(unsigned)grid, cfg.threads, smem, stream>>>(a);
     return check_launch(stream, "staged kernel launch");
+}
+
+// Launches one batch kernel over tensors that all qualify for it.
+static int launch_batch_kernel(const pfhe_tensor_desc *d, const int *idx, int count, cudaStream_t stream, int dev, int sms,
+                               const pfhe_launch_cfg *cfg)
+{
+    const int threads = cfg && cfg->threads > 0 ? cfg->threads : 256;
+    const int cps = cfg && cfg->ctas_per_sm > 0 ? cfg->ctas_per_sm : 2;
+    const int target = cfg && cfg->tile_blocks > 0 ? cfg->tile_blocks : 512;
+    BatchKernelArgs a;
+    memset(&a, 0, sizeof a);
+    int64_t blocks = 0;
+    for (int i = 0; i < count; ++i) {
+        const pfhe_tensor_desc &t = d[idx[i]];
+        int be = 0, bb = 0;
+        type_geometry(t.ggml_type, &be, &bb);
+        fill_packed(&a.t[i], static_cast<const uint8_t *>(t.src_dev), t.dst_dev, t.n_elements, bb);
+        a.t[i].kind = t.ggml_type * 4 + t.out_dtype;
+        blocks += a.t[i].n_blocks;
+    }
+    a.n_tensors = count;
+    a.stages = cfg && cfg->stages > 0 ? cfg->stages : 4;
+    int rc;
+    if ((rc = status_word(dev, &a.status))) return rc;
+    const int64_t max_ctas = (int64_t)sms * cps;
+    const int64_t groups = (blocks + 7) / 8;
+    const int64_t grid = groups < max_ctas ? groups : max_ctas;
+    int max_tile = (int)((kSmemBudget / (size_t)cps - 1024) / ((size_t)a.stages * 34) - 16) / 8 * 8;
+    if (max_tile > 2048) max_tile = 2048;
+    a.tile_blocks = balanced_tile_blocks(blocks, grid, target, max_tile);
+    int64_t tiles = 0;
+    for (int i = 0; i < count; ++i) {
+        a.tile_prefix[i] = tiles;
+        tiles += (a.t[i].n_blocks + a.tile_blocks - 1) / a.tile_blocks;
+    }
+    a.tile_prefix[count] = tiles;
+    const int64_t tiles_per_cta = (tiles + grid - 1) / grid;
+    if (tiles_per_cta < a.stages) a.stages = (int)tiles_per_cta;
+    const size_t smem = (size_t)a.stages * (a.tile_blocks * 34 + 16);
+    auto fn = dequant_blocks_batch<true>;
+    if ((rc = ensure_smem(reinterpret_cast<const void *>(fn), dev, smem))) return rc;
+    fn<<<(unsigned)(tiles < grid ? tiles : grid), threads, smem, stream>>>(a);
+    return check_launch(stream, "batch kernel launch");
+}
+
+int launch_batch(const pfhe_tensor_desc *d, int n, cudaStream_t stream, const pfhe_launch_cfg *cfg)
+{
+    if (cfg && (cfg->threads % 32 || cfg->threads > 512 || cfg->stages > kMaxStages)) { set_error("bad launch configuration"); return PFHE_ERR_BAD_ARG; }
+    if (n < 0 || (n > 0 && !d)) { set_error("bad batch arguments"); return PFHE_ERR_BAD_ARG; }
+    int dev = 0, sms = 0, rc;
+    // Validate everything before launching anything.
+    for (int i = 0; i < n; ++i) {
+        int be = 0, bb = 0;
+        if ((rc = type_geometry(d[i].ggml_type, &be, &bb))) return rc;
+        const int osz = out_size(d[i].out_dtype);
+        if (osz == 0) { set_error("tensor %d: output dtype %d not in {f32,f16,bf16}", i, d[i].out_dtype); return PFHE_ERR_BAD_DTYPE; }
+        if (d[i].n_elements < 0 || d[i].src_bytes < 0 || d[i].dst_bytes < 0) { set_error("tensor %d: negative size", i); return PFHE_ERR_BAD_ARG; }
+        const int64_t need = (d[i].n_elements + be - 1) / be * bb;
+        if (d[i].src_bytes < need) { set_error("tensor %d: Data too short: %lld < %lld", i, (long long)d[i].src_bytes, (long long)need); return PFHE_ERR_SHORT_SOURCE; }
+        if (d[i].dst_bytes < d[i].n_elements * osz) { set_error("tensor %d: destination too small", i); return PFHE_ERR_SHORT_DEST; }
+        if (d[i].n_elements > 0 && (!d[i].src_dev || !d[i].dst_dev)) { set_error("tensor %d: null device pointer", i); return PFHE_ERR_BAD_ARG; }
+    }
+    if (n == 0) return PFHE_OK;
+    if ((rc = current_device(&dev))) return rc;
+    if ((rc = sm_count(dev, &sms))) return rc;
+
+    int idx[kMaxBatch];
+    int count = 0;
+    for (int i = 0; i < n; ++i) {
+        const pfhe_tensor_desc &t = d[i];
+        if (t.n_elements == 0) continue;
+        int be = 0, bb = 0;
+        type_geometry(t.ggml_type, &be, &bb);
+        const bool batchable = be == 32 && reinterpret_cast<uintptr_t>(t.src_dev) % 2 == 0 &&
+                               reinterpret_cast<uintptr_t>(t.dst_dev) % 16 == 0;
+        if (!batchable) {
+            rc = launch_decode(t.ggml_type, t.out_dtype, t.out_dtype, t.src_dev, t.src_bytes, t.dst_dev, t.dst_bytes,
+                               t.n_elements, stream, nullptr);
+            if (rc) return rc;
+            continue;
+        }
+        idx[count++] = i;
+        if (count == kMaxBatch) {
+            if ((rc = launch_batch_kernel(d, idx, count, stream, dev, sms, cfg))) return rc;
+            count = 0;
+        }
+    }
+    if (count == 1) {
+        const pfhe_tensor_desc &t = d[idx[0]];
+        return launch_decode(t.ggml_type, t.out_dtype, t.out_dtype, t.src_dev, t.src_bytes, t.dst_dev, t.dst_bytes,
+                             t.n_elements, stream, nullptr);
+    }
+    if (count > 1) return launch_batch_kernel(d, idx, count, stream, dev, sms, cfg);
+    return PFHE_OK;
 }
 
 }  // namespace pfhe
@@ -334,6 +469,16 @@ int pfhe_dequant_launch_ex(int ggml_type, int mid_dtype, int out_dtype, const vo
 {
     return launch_decode(ggml_type, mid_dtype, out_dtype, src_dev, src_bytes, dst_dev, dst_bytes, n_elements,
                          static_cast<cudaStream_t>(stream), cfg);
+}
+
+int pfhe_dequant_launch_batch(const pfhe_tensor_desc *tensors, int n_tensors, void *stream)
+{
+    return launch_batch(tensors, n_tensors, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int pfhe_dequant_launch_batch_ex(const pfhe_tensor_desc *tensors, int n_tensors, void *stream, const pfhe_launch_cfg *cfg)
+{
+    return launch_batch(tensors, n_tensors, static_cast<cudaStream_t>(stream), cfg);
 }
 
 int pfhe_device_status(int device)

@@ -341,104 +341,250 @@ template <bool kStream> __device__ __forceinline__ void store16(void *p, uint4 v
 constexpr uint64_t kDeviceWaitLimitNs = 2000000000ull;   // 2 s: far beyond any healthy copy
 constexpr int kMaxStages = 8;
 
-struct BlockKernelArgs {
+// One quantised tensor (or row slice) as the staged kernels see it.
+struct PackedTensor {
     const uint8_t *src16;   // source rounded down to a 16-byte line
-    int32_t skew;           // src - src16 (even, 0..14)
     void *dst;              // 16-byte aligned
     int64_t n_elements;
     int64_t n_blocks;       // ceil(n_elements / 32)
     int64_t span_bytes;     // bytes from src16 to the 16-byte-rounded end of the packed data
+    int32_t skew;           // src - src16 (even, 0..14)
+    int32_t kind;           // batch kernel only: ggml type * 4 + output dtype
+};
+
+struct BlockKernelArgs {
+    PackedTensor t;
     int32_t tile_blocks;    // multiple of 8
     int32_t stages;         // 1..kMaxStages
+    int32_t interleaved;    // 0: each CTA owns one contiguous run; 1: tiles dealt round-robin to CTAs
     int *status;            // device-visible status word (pinned host memory)
 };
 
-// ---------------------------------------------------------------------------
-// Variant 1: bulk-copy staged tiles in, coalesced 16-byte stores out.
-// Each CTA owns one contiguous run of 8-block groups and walks it in tiles of
-// `tile_blocks` blocks through a `stages`-deep ring of shared-memory buffers.
-// ---------------------------------------------------------------------------
+// Per-CTA ring of shared-memory stages fed by bulk copies.  The parity each
+// stage's barrier will complete next is kept in a register bit mask, so the
+// ring can be reused for any number of runs.
+struct StageRing {
+    uint8_t *smem;
+    uint64_t *full;
+    int stages;
+    int stage_bytes;
+    uint32_t parity_bits;
+};
+
+// Decodes one staged tile: blocks [tb0, tb0 + nb) of `pt`, whose packed bytes
+// start at `tile` in shared memory.  Called by every thread of the CTA.
 template <int T, int MID, int OUT, bool kStream>
-__global__ void __launch_bounds__(512) dequant_blocks_staged(const BlockKernelArgs a)
+__device__ __forceinline__ void decode_tile(const PackedTensor &pt, int64_t tb0, int nb, const uint8_t *tile)
 {
     constexpr int BB = Fmt<T>::kBytes;
     constexpr int VEC = 16 / OutT<OUT>::kSize;       // outputs per 16-byte store
     constexpr int UPB = 32 / VEC;                    // units per block
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full[kMaxStages];
+    const int64_t e0 = tb0 << 5;
+    const int64_t rem = pt.n_elements - e0;                        // > 0
+    const int tile_elems = nb << 5;
+    const int valid = rem < tile_elems ? (int)rem : tile_elems;
+    const int full_units = valid / VEC;
+    uint8_t *out = reinterpret_cast<uint8_t *>(pt.dst) + e0 * OutT<OUT>::kSize;
 
-    const int stage_bytes = a.tile_blocks * BB + 16;
-    const int64_t n_groups = (a.n_blocks + 7) >> 3;
-    const int64_t g0 = n_groups * blockIdx.x / gridDim.x;
-    const int64_t g1 = n_groups * (blockIdx.x + 1) / gridDim.x;
-    const int64_t b0 = g0 << 3;
-    const int64_t b1 = (g1 << 3) < a.n_blocks ? (g1 << 3) : a.n_blocks;
-    if (b1 <= b0) return;
-    const int n_tiles = (int)((b1 - b0 + a.tile_blocks - 1) / a.tile_blocks);
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+#pragma unroll 4
+    for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
+        const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
+        store16<kStream>(out + (size_t)u * 16, r);
     }
-    __syncthreads();
+    // Ragged end of the tensor (n_elements not a multiple of VEC): scalar stores.
+    if (valid % VEC != 0 && threadIdx.x == 0) {
+        for (int e = full_units * VEC; e < valid; ++e)
+            store_scalar<MID, OUT>(pt.dst, e0 + e, decode_element_bytes<T>(tile, e));
+    }
+}
 
-    auto issue = [&](int t) {
-        const int s = t % a.stages;
-        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
-        const int64_t nb = (b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks;
-        const int64_t off = tb0 * BB;                              // multiple of 16
-        int64_t bytes = (nb * BB + a.skew + 15) & ~(int64_t)15;
-        if (off + bytes > a.span_bytes) bytes = a.span_bytes - off;
-        mbar_expect_tx(&full[s], (uint32_t)bytes);
-        bulk_g2s(smem + (size_t)s * stage_bytes, a.src16 + off, (uint32_t)bytes, &full[s]);
+// Decodes the tiles {first + k*stride : k >= 0, first + k*stride < end} (block
+// indices) of tensor `pt`, each tile min(tile_blocks, end - start) blocks long.
+// Every thread of the CTA must call this with the same arguments.  Returns
+// false when a bounded barrier wait ran out (after giving copies already in
+// flight a bounded chance to land).
+template <int T, int MID, int OUT, bool kStream>
+__device__ __forceinline__ bool decode_run(const PackedTensor &pt, int64_t first, int64_t stride, int64_t end,
+                                           int tile_blocks, StageRing &ring)
+{
+    constexpr int BB = Fmt<T>::kBytes;
+    if (first >= end) return true;
+    const int n_tiles = (int)((end - first + stride - 1) / stride);
+
+    auto issue = [&](int k) {
+        const int s = k % ring.stages;
+        const int64_t tb0 = first + (int64_t)k * stride;
+        const int64_t nb = (end - tb0) < tile_blocks ? (end - tb0) : tile_blocks;
+        const int64_t off = tb0 * BB;                              // multiple of 16: tb0 is a multiple of 8
+        int64_t bytes = (nb * BB + pt.skew + 15) & ~(int64_t)15;
+        if (off + bytes > pt.span_bytes) bytes = pt.span_bytes - off;
+        mbar_expect_tx(&ring.full[s], (uint32_t)bytes);
+        bulk_g2s(ring.smem + (size_t)s * ring.stage_bytes, pt.src16 + off, (uint32_t)bytes, &ring.full[s]);
     };
 
     if (threadIdx.x == 0) {
-        const int pre = n_tiles < a.stages ? n_tiles : a.stages;
-        for (int t = 0; t < pre; ++t) issue(t);
+        const int pre = n_tiles < ring.stages ? n_tiles : ring.stages;
+        for (int k = 0; k < pre; ++k) issue(k);
     }
 
-    int waited_ok = 1;
-    int t = 0;
-    for (; t < n_tiles; ++t) {
-        const int s = t % a.stages;
-        const uint32_t parity = (uint32_t)(t / a.stages) & 1u;
-        if (!mbar_wait_bounded(&full[s], parity, kDeviceWaitLimitNs)) waited_ok = 0;
+    int k = 0;
+    for (; k < n_tiles; ++k) {
+        const int s = k % ring.stages;
+        const bool ok = mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs);
         // Every thread must agree before touching the tile or leaving the loop.
-        if (__syncthreads_or(!waited_ok)) break;
+        if (__syncthreads_or(!ok)) break;
+        ring.parity_bits ^= 1u << s;
 
-        const uint8_t *tile = smem + (size_t)s * stage_bytes + a.skew;
-        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
-        const int nb = (int)((b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks);
-        const int64_t e0 = tb0 << 5;
-        int64_t rem = a.n_elements - e0;                           // > 0
-        const int tile_elems = nb << 5;
-        const int valid = rem < tile_elems ? (int)rem : tile_elems;
-        const int full_units = valid / VEC;
-        uint8_t *out = reinterpret_cast<uint8_t *>(a.dst) + e0 * OutT<OUT>::kSize;
-
-#pragma unroll 4
-        for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
-            const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
-            store16<kStream>(out + (size_t)u * 16, r);
-        }
-        // Ragged end of the tensor (n_elements not a multiple of VEC): scalar stores.
-        if (valid % VEC != 0 && threadIdx.x == 0) {
-            for (int e = full_units * VEC; e < valid; ++e)
-                store_scalar<MID, OUT>(a.dst, e0 + e, decode_element_bytes<T>(tile, e));
-        }
+        const int64_t tb0 = first + (int64_t)k * stride;
+        const int nb = (int)((end - tb0) < tile_blocks ? (end - tb0) : tile_blocks);
+        decode_tile<T, MID, OUT, kStream>(pt, tb0, nb, ring.smem + (size_t)s * ring.stage_bytes + pt.skew);
         __syncthreads();                                           // all reads of stage s done
-        if (threadIdx.x == 0 && t + a.stages < n_tiles) issue(t + a.stages);
+        if (threadIdx.x == 0 && k + ring.stages < n_tiles) issue(k + ring.stages);
+    }
+    if (k == n_tiles) return true;
+
+    // A wait ran out: give the copies already issued a bounded chance to land
+    // before the caller releases the shared memory.
+    if (threadIdx.x == 0) {
+        const int last = (k + ring.stages) < n_tiles ? (k + ring.stages) : n_tiles;
+        for (int j = k; j < last; ++j) {
+            const int s = j % ring.stages;
+            (void)mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs / 8);
+        }
+    }
+    __syncthreads();
+    return false;
+}
+
+__device__ __forceinline__ void ring_init(StageRing &ring, uint8_t *smem, uint64_t *full, int stages, int stage_bytes)
+{
+    ring.smem = smem;
+    ring.full = full;
+    ring.stages = stages;
+    ring.stage_bytes = stage_bytes;
+    ring.parity_bits = 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// Variant 1: bulk-copy staged tiles in, coalesced 16-byte stores out, one tensor.
+// ---------------------------------------------------------------------------
+template <int T, int MID, int OUT, bool kStream>
+__global__ void __launch_bounds__(512) dequant_blocks_staged(const BlockKernelArgs a)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full[kMaxStages];
+    StageRing ring;
+    ring_init(ring, smem, full, a.stages, a.tile_blocks * Fmt<T>::kBytes + 16);
+
+    bool ok;
+    if (a.interleaved) {
+        ok = decode_run<T, MID, OUT, kStream>(a.t, (int64_t)blockIdx.x * a.tile_blocks, (int64_t)gridDim.x * a.tile_blocks,
+                                              a.t.n_blocks, a.tile_blocks, ring);
+    } else {
+        const int64_t n_groups = (a.t.n_blocks + 7) >> 3;
+        const int64_t b0 = (n_groups * blockIdx.x / gridDim.x) << 3;
+        int64_t b1 = (n_groups * (blockIdx.x + 1) / gridDim.x) << 3;
+        if (b1 > a.t.n_blocks) b1 = a.t.n_blocks;
+        ok = decode_run<T, MID, OUT, kStream>(a.t, b0, a.tile_blocks, b1, a.tile_blocks, ring);
+    }
+    if (!ok && threadIdx.x == 0) atomicExch(a.status, DEV_WAIT_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------
+// Batch kernel: up to kMaxBatch quantised tensors of mixed formats in ONE
+// launch.  Every tensor is cut into tiles of `tile_blocks` blocks; the tiles of
+// all tensors form one sequence that is dealt round-robin to the CTAs, and each
+// CTA prefetches `stages` tiles ahead across tensor boundaries.  Sixteen 100 MB
+// tensors therefore cost one launch ramp instead of sixteen.  MID == OUT only.
+// ---------------------------------------------------------------------------
+constexpr int kMaxBatch = 32;
+
+struct BatchKernelArgs {
+    PackedTensor t[kMaxBatch];
+    int64_t tile_prefix[kMaxBatch + 1];    // tile_prefix[i] = tiles before tensor i
+    int32_t n_tensors;
+    int32_t tile_blocks;
+    int32_t stages;
+    int *status;
+};
+
+__device__ __forceinline__ int kind_block_bytes(int kind)
+{
+    const int t = kind >> 2;
+    return t == T_Q4_0 ? 18 : (t == T_Q4_1 ? 20 : 34);
+}
+
+template <bool kStream>
+__global__ void __launch_bounds__(512) dequant_blocks_batch(const __grid_constant__ BatchKernelArgs a)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full[kMaxStages];
+    StageRing ring;
+    ring_init(ring, smem, full, a.stages, a.tile_blocks * 34 + 16);     // sized for the widest block
+
+    const int64_t total_tiles = a.tile_prefix[a.n_tensors];
+    if ((int64_t)blockIdx.x >= total_tiles) return;
+    const int n_my = (int)((total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+
+    int ti_issue = 0;                                                   // thread 0's cursor for prefetches
+    auto issue = [&](int j) {
+        const int64_t g = blockIdx.x + (int64_t)j * gridDim.x;
+        while (g >= a.tile_prefix[ti_issue + 1]) ++ti_issue;
+        const PackedTensor &pt = a.t[ti_issue];
+        const int bbytes = kind_block_bytes(pt.kind);
+        const int s = j % ring.stages;
+        const int64_t tb0 = (g - a.tile_prefix[ti_issue]) * a.tile_blocks;
+        const int64_t nb = (pt.n_blocks - tb0) < a.tile_blocks ? (pt.n_blocks - tb0) : a.tile_blocks;
+        const int64_t off = tb0 * bbytes;
+        int64_t bytes = (nb * bbytes + pt.skew + 15) & ~(int64_t)15;
+        if (off + bytes > pt.span_bytes) bytes = pt.span_bytes - off;
+        mbar_expect_tx(&ring.full[s], (uint32_t)bytes);
+        bulk_g2s(ring.smem + (size_t)s * ring.stage_bytes, pt.src16 + off, (uint32_t)bytes, &ring.full[s]);
+    };
+    if (threadIdx.x == 0) {
+        const int pre = n_my < ring.stages ? n_my : ring.stages;
+        for (int j = 0; j < pre; ++j) issue(j);
     }
 
-    if (t < n_tiles) {
-        // A wait ran out.  Report it, then give copies already issued a bounded
-        // chance to land before the shared memory is released.
+    int ti = 0;
+    int j = 0;
+    for (; j < n_my; ++j) {
+        const int s = j % ring.stages;
+        const bool ok = mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs);
+        if (__syncthreads_or(!ok)) break;
+        ring.parity_bits ^= 1u << s;
+
+        const int64_t g = blockIdx.x + (int64_t)j * gridDim.x;
+        while (g >= a.tile_prefix[ti + 1]) ++ti;
+        const PackedTensor &pt = a.t[ti];
+        const int64_t tb0 = (g - a.tile_prefix[ti]) * a.tile_blocks;
+        const int nb = (int)((pt.n_blocks - tb0) < a.tile_blocks ? (pt.n_blocks - tb0) : a.tile_blocks);
+        const uint8_t *tile = ring.smem + (size_t)s * ring.stage_bytes + pt.skew;
+        switch (pt.kind) {
+#define PFHE_TILE(TT, OO) case TT * 4 + OO: decode_tile<TT, OO, OO, kStream>(pt, tb0, nb, tile); break;
+            PFHE_TILE(T_Q4_0, O_F32) PFHE_TILE(T_Q4_0, O_F16) PFHE_TILE(T_Q4_0, O_BF16)
+            PFHE_TILE(T_Q4_1, O_F32) PFHE_TILE(T_Q4_1, O_F16) PFHE_TILE(T_Q4_1, O_BF16)
+            PFHE_TILE(T_Q8_0, O_F32) PFHE_TILE(T_Q8_0, O_F16) PFHE_TILE(T_Q8_0, O_BF16)
+#undef PFHE_TILE
+            default: break;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && j + ring.stages < n_my) issue(j + ring.stages);
+    }
+    if (j < n_my) {
+        // A wait ran out: report it and give copies in flight a bounded chance to land.
         if (threadIdx.x == 0) {
             atomicExch(a.status, DEV_WAIT_TIMEOUT);
-            const int last = (t + a.stages) < n_tiles ? (t + a.stages) : n_tiles;
-            for (int k = t; k < last; ++k)
-                (void)mbar_wait_bounded(&full[k % a.stages], (uint32_t)(k / a.stages) & 1u, kDeviceWaitLimitNs / 8);
+            const int last = (j + ring.stages) < n_my ? (j + ring.stages) : n_my;
+            for (int q = j; q < last; ++q) {
+                const int s = q % ring.stages;
+                (void)mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs / 8);
+            }
         }
         __syncthreads();
     }
@@ -462,11 +608,11 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKern
     const int stage_bytes = a.tile_blocks * BB + 16;
     const int out_tile_bytes = a.tile_blocks * 32 * OutT<OUT>::kSize;
     uint8_t *out_smem = smem + (((size_t)a.stages * stage_bytes + 127) & ~(size_t)127);   // two buffers
-    const int64_t n_groups = (a.n_blocks + 7) >> 3;
+    const int64_t n_groups = (a.t.n_blocks + 7) >> 3;
     const int64_t g0 = n_groups * blockIdx.x / gridDim.x;
     const int64_t g1 = n_groups * (blockIdx.x + 1) / gridDim.x;
     const int64_t b0 = g0 << 3;
-    const int64_t b1 = (g1 << 3) < a.n_blocks ? (g1 << 3) : a.n_blocks;
+    const int64_t b1 = (g1 << 3) < a.t.n_blocks ? (g1 << 3) : a.t.n_blocks;
     if (b1 <= b0) return;
     const int n_tiles = (int)((b1 - b0 + a.tile_blocks - 1) / a.tile_blocks);
 
@@ -481,10 +627,10 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKern
         const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
         const int64_t nb = (b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks;
         const int64_t off = tb0 * BB;
-        int64_t bytes = (nb * BB + a.skew + 15) & ~(int64_t)15;
-        if (off + bytes > a.span_bytes) bytes = a.span_bytes - off;
+        int64_t bytes = (nb * BB + a.t.skew + 15) & ~(int64_t)15;
+        if (off + bytes > a.t.span_bytes) bytes = a.t.span_bytes - off;
         mbar_expect_tx(&full[s], (uint32_t)bytes);
-        bulk_g2s(smem + (size_t)s * stage_bytes, a.src16 + off, (uint32_t)bytes, &full[s]);
+        bulk_g2s(smem + (size_t)s * stage_bytes, a.t.src16 + off, (uint32_t)bytes, &full[s]);
     };
 
     if (threadIdx.x == 0) {
@@ -502,16 +648,16 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKern
         if (threadIdx.x == 0) bulk_wait_read<1>();
         if (__syncthreads_or(!waited_ok)) break;
 
-        const uint8_t *tile = smem + (size_t)s * stage_bytes + a.skew;
+        const uint8_t *tile = smem + (size_t)s * stage_bytes + a.t.skew;
         uint8_t *obuf = out_smem + (size_t)(t & 1) * out_tile_bytes;
         const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
         const int nb = (int)((b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks);
         const int64_t e0 = tb0 << 5;
-        const int64_t rem = a.n_elements - e0;
+        const int64_t rem = a.t.n_elements - e0;
         const int tile_elems = nb << 5;
         const int valid = rem < tile_elems ? (int)rem : tile_elems;
         const int full_units = valid / VEC;
-        uint8_t *gout = reinterpret_cast<uint8_t *>(a.dst) + e0 * OutT<OUT>::kSize;
+        uint8_t *gout = reinterpret_cast<uint8_t *>(a.t.dst) + e0 * OutT<OUT>::kSize;
         const bool bulk_ok = (valid == tile_elems);               // whole blocks only: byte count is a multiple of 64
 
         if (bulk_ok) {
@@ -534,7 +680,7 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKern
             }
             if (valid % VEC != 0 && threadIdx.x == 0) {
                 for (int e = full_units * VEC; e < valid; ++e)
-                    store_scalar<MID, OUT>(a.dst, e0 + e, decode_element_bytes<T>(tile, e));
+                    store_scalar<MID, OUT>(a.t.dst, e0 + e, decode_element_bytes<T>(tile, e));
             }
             __syncthreads();
             if (threadIdx.x == 0 && t + a.stages < n_tiles) issue(t + a.stages);

@@ -176,3 +176,79 @@ def test_decode_is_idempotent_and_launches_are_counted():
     b = decode_on_gpu(FORMATS["Q4_1"], raw, numel, "bf16")
     assert L.pfhe_launch_count() == before + 2
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+# --- batch entry point ------------------------------------------------------------------------
+def _batch_case(fmt, numel, seed):
+    raw = synth.random_packed(FORMATS[fmt], numel, np.random.default_rng(seed))
+    return fmt, raw, numel
+
+
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+def test_batch_matches_single_launches_and_oracle(dtype):
+    from gpu_util import TORCH_DT, device_bytes
+    from pfhe_b200.resident import decode_resident
+    cases = [_batch_case("Q4_0", 11008 * 64, 1), _batch_case("Q4_1", 4096 * 33, 2), _batch_case("Q8_0", 32 * 7 + 5, 3),
+             _batch_case("F32", 4096, 4), _batch_case("Q4_0", 1, 5), _batch_case("BF16", 777, 6),
+             _batch_case("Q8_0", 4096 * 128, 7), _batch_case("Q4_1", 32 * 8 * 1000 + 32, 8), _batch_case("F16", 8192, 9)]
+    cases += [_batch_case(("Q4_0", "Q4_1", "Q8_0")[i % 3], 32 * (50 + 13 * i), 20 + i) for i in range(40)]   # > 32 per launch
+    skews = [0, 2, 6, 0, 14, 0, 4, 0, 0] + [(2 * i) % 16 for i in range(40)]
+    items = [(device_bytes(raw, sk), FORMATS[fmt], (numel,)) for (fmt, raw, numel), sk in zip(cases, skews)]
+    outs = decode_resident(items, TORCH_DT[dtype])
+    torch.cuda.synchronize()
+    _native.check(_native.lib().pfhe_device_status(-1))
+    for (fmt, raw, numel), got in zip(cases, outs):
+        want = np_oracle.read_tensor(FORMATS[fmt], raw, numel, dtype)
+        assert_same_bits(to_bits(got), want, dtype, f"batch {fmt} n={numel}->{dtype}")
+
+
+def test_batch_of_config2_tensors():
+    from gpu_util import device_bytes
+    from pfhe_b200.resident import decode_resident
+    raw0, numel = _config_tensor("Q4_0", (11008, 4096), 2)
+    raw1, _ = _config_tensor("Q4_1", (11008, 4096), 3)
+    want0 = c_oracle.read_tensor(FORMATS["Q4_0"], raw0, numel, "f16", n_threads=8)
+    want1 = c_oracle.read_tensor(FORMATS["Q4_1"], raw1, numel, "f16", n_threads=8)
+    items = [(device_bytes(raw0), FORMATS["Q4_0"], (11008, 4096)), (device_bytes(raw1), FORMATS["Q4_1"], (11008, 4096))] * 3
+    before = _native.lib().pfhe_launch_count()
+    outs = decode_resident(items, torch.float16)
+    assert _native.lib().pfhe_launch_count() == before + 1
+    for i, got in enumerate(outs):
+        assert tuple(got.shape) == (11008, 4096)
+        assert_same_bits(to_bits(got), want0 if i % 2 == 0 else want1, "f16", f"batch item {i}")
+
+
+def test_batch_validation_launches_nothing_on_error():
+    L = _native.lib()
+    src = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    dst = torch.ones(1024, dtype=torch.float16, device="cuda")
+    descs = (_native.TensorDesc * 2)()
+    descs[0] = _native.TensorDesc(2, 1, src.data_ptr(), 18 * 8, dst.data_ptr(), 512, 256)
+    descs[1] = _native.TensorDesc(2, 1, src.data_ptr(), 17, dst.data_ptr(), 512, 32)          # short source
+    before = L.pfhe_launch_count()
+    assert L.pfhe_dequant_launch_batch(descs, 2, None) == _native.ERR_SHORT_SOURCE
+    assert "tensor 1" in _native.last_error()
+    assert L.pfhe_launch_count() == before
+    torch.cuda.synchronize()
+    assert bool((dst == 1).all())
+    assert L.pfhe_dequant_launch_batch(descs, 0, None) == 0
+
+
+@pytest.mark.parametrize("schedule", [0, 1, 2])
+@pytest.mark.parametrize("exact_tiles", [0, 1])
+def test_tile_schedules(schedule, exact_tiles):
+    import ctypes
+    from gpu_util import device_bytes
+    raw, numel = _config_tensor("Q8_0", (1000, 4096), 5)
+    want = c_oracle.read_tensor(FORMATS["Q8_0"], raw, numel, "bf16", n_threads=4)
+    L = _native.lib()
+    src = device_bytes(raw, 6)
+    dst = torch.empty(numel, dtype=torch.bfloat16, device="cuda")
+    c = _native.LaunchCfg(variant=1, tile_blocks=64, stages=3, threads=128, ctas_per_sm=2, streaming_stores=1)
+    c.reserved[0] = schedule
+    c.reserved[1] = exact_tiles
+    _native.check(L.pfhe_dequant_launch_ex(8, 2, 2, src.data_ptr(), src.numel(), dst.data_ptr(), numel * 2, numel,
+                                           torch.cuda.current_stream().cuda_stream, ctypes.byref(c)))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    assert_same_bits(to_bits(dst), want, "bf16", f"schedule {schedule} exact {exact_tiles}")
