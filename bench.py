@@ -33,6 +33,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 Q4_0, Q4_1, Q8_0 = 2, 3, 8
+# dram__bytes_read.sum + dram__bytes_write.sum of one dequant_blocks_batch launch over the default step
+# (16 tensors), from the ncu capture summarised in profiles/dequant_blocks_batch_q4_0_f16_16x11008x4096.md
+NCU_TRAFFIC_BYTES_16 = 405.89e6 + 1383.7e6
 ROWS, COLS = 11008, 4096
 NUMEL = ROWS * COLS
 METRIC = "dequant_output_gbps_q4_0_11008x4096_to_fp16"
@@ -266,29 +269,31 @@ def run_gpu_arm(args) -> None:
     torch.cuda.synchronize()
     single_launch_ms = a.elapsed_time(b) / (max(args.steps // 2, 2) * batch)
 
-    # --- other formats of the same shape, same method (reported, not the headline) ----------
+    # --- other formats of the same shape, same method: one batch launch per step (reported, not the headline) ---
     per_format = {}
     for name, t, odt, oid in (("Q4_1->f16", Q4_1, torch.float16, _native.OUT_F16), ("Q8_0->f16", Q8_0, torch.float16, _native.OUT_F16),
-                              ("Q4_0->bf16", Q4_0, torch.bfloat16, _native.OUT_BF16), ("Q4_1->bf16", Q4_1, torch.bfloat16, _native.OUT_BF16)):
+                              ("Q4_0->bf16", Q4_0, torch.bfloat16, _native.OUT_BF16), ("Q4_1->bf16", Q4_1, torch.bfloat16, _native.OUT_BF16),
+                              ("Q8_0->bf16", Q8_0, torch.bfloat16, _native.OUT_BF16)):
         nb = L.pfhe_tensor_nbytes(t, NUMEL)
-        fs = [torch.from_numpy(synth.random_packed(t, NUMEL, np.random.default_rng([3, rank, i]))).to(dev) for i in range(4)]
-        fs = [fs[i % 4] if i < 4 else fs[i % 4].clone() for i in range(batch)]
-        fd = [d.view(odt) for d in dsts]
-        def fstep():
-            for s, d in zip(fs, fd):
-                L.pfhe_dequant_launch(t, oid, s.data_ptr(), nb, d.data_ptr(), out_bytes, NUMEL, stream.cuda_stream)
+        base = [torch.from_numpy(synth.random_packed(t, NUMEL, np.random.default_rng([3, rank, i]))).to(dev) for i in range(2)]
+        fs = [base[i] if i < 2 else base[i % 2].clone() for i in range(batch)]
+        fdesc = (_native.TensorDesc * batch)()
+        for i, (s_, d_) in enumerate(zip(fs, dsts)):
+            fdesc[i] = _native.TensorDesc(t, oid, s_.data_ptr(), nb, d_.data_ptr(), out_bytes, NUMEL)
         for _ in range(3):
-            fstep()
+            L.pfhe_dequant_launch_batch(fdesc, batch, stream.cuda_stream)
         torch.cuda.synchronize()
+        reps = max(args.steps // 2, 2)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
-        for _ in range(max(args.steps // 2, 2)):
-            fstep()
+        for _ in range(reps):
+            L.pfhe_dequant_launch_batch(fdesc, batch, stream.cuda_stream)
         b.record(stream)
         torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / (max(args.steps // 2, 2) * batch)
-        per_format[name] = {"output_gbps": out_bytes / ms / 1e6, "hbm_gbps": (nb + out_bytes) / ms / 1e6}
-        del fs
+        ms = a.elapsed_time(b) / (reps * batch)
+        per_format[name] = {"output_gbps": out_bytes / ms / 1e6, "hbm_gbps": (nb + out_bytes) / ms / 1e6,
+                            "frac_of_measured_peak": (nb + out_bytes) / ms / 1e6 / measured_peaks()[0]}
+        del fs, base
 
     # --- end to end through the public API: GGUF file on the host -> device tensors ----------
     e2e = run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch)
@@ -321,7 +326,8 @@ def run_gpu_arm(args) -> None:
                        "l2": f"inputs larger than L2: {batch} distinct tensors, {batch * algo_bytes / 1e6:.0f} MB touched per step",
                        "in_bytes_per_tensor": in_bytes, "out_bytes_per_tensor": out_bytes},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": args.traffic_bytes, "peak_kind": peak_kind,
+                         "traffic": args.traffic_bytes if args.traffic_bytes else (NCU_TRAFFIC_BYTES_16 if batch == 16 else None),
+                         "peak_kind": peak_kind,
                          "kernel": "dequant_blocks_batch", "launches_per_step": launches_per_step,
                          "algorithmic_bytes_per_launch": algo_bytes * batch // launches_per_step, "launch_ms": launch_ms,
                          "frac_of_nominal_8000": achieved / 8000.0,
@@ -391,7 +397,8 @@ def run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch):
 def run_kernel_case(spec: str) -> None:
     """A few launches of one decode kernel on device-resident data (the case profilers capture).
 
-    spec = FORMAT:OUT:NUMEL[:LAUNCHES], e.g. Q4_0:f16:134217728:6
+    spec = FORMAT:OUT:NUMEL[:LAUNCHES[:BATCH]], e.g. Q4_0:f16:134217728:6 (one tensor per launch,
+    pfhe_dequant_launch) or Q4_0:f16:45088768:4:16 (BATCH tensors per launch, pfhe_dequant_launch_batch).
     """
     import torch
     from pfhe_b200 import _native, synth
@@ -400,27 +407,36 @@ def run_kernel_case(spec: str) -> None:
     oid, odt = {"f32": (0, torch.float32), "f16": (1, torch.float16), "bf16": (2, torch.bfloat16)}[parts[1]]
     numel = int(parts[2])
     launches = int(parts[3]) if len(parts) > 3 else 6
+    nbatch = int(parts[4]) if len(parts) > 4 else 1
     L = _native.lib()
     nb = L.pfhe_tensor_nbytes(fmt, numel)
     chunk = 1 << 22
     tile = torch.from_numpy(synth.random_packed(fmt, chunk, np.random.default_rng(1))).cuda()
     reps = -(-nb // tile.numel())
     src = tile.repeat(reps)[:nb].contiguous()
-    dsts = [torch.empty(numel, dtype=odt, device="cuda") for _ in range(2)]
+    srcs = [src] + [src.clone() for _ in range(nbatch - 1)]
+    dsts = [torch.empty(numel, dtype=odt, device="cuda") for _ in range(max(2, nbatch))]
+    descs = (_native.TensorDesc * nbatch)()
+    for i in range(nbatch):
+        descs[i] = _native.TensorDesc(fmt, oid, srcs[i].data_ptr(), nb, dsts[i].data_ptr(),
+                                      numel * dsts[0].element_size(), numel)
     st = torch.cuda.current_stream()
     evs = []
     for i in range(launches):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(st)
-        _native.check(L.pfhe_dequant_launch(fmt, oid, src.data_ptr(), nb, dsts[i & 1].data_ptr(),
-                                            numel * dsts[0].element_size(), numel, st.cuda_stream))
+        if nbatch > 1:
+            _native.check(L.pfhe_dequant_launch_batch(descs, nbatch, st.cuda_stream))
+        else:
+            _native.check(L.pfhe_dequant_launch(fmt, oid, src.data_ptr(), nb, dsts[i & 1].data_ptr(),
+                                                numel * dsts[0].element_size(), numel, st.cuda_stream))
         b.record(st)
         evs.append((a, b))
     torch.cuda.synchronize()
     _native.check(L.pfhe_device_status(-1))
     ms = sorted(a.elapsed_time(b) for a, b in evs[1:])[len(evs[1:]) // 2]
-    total = nb + numel * dsts[0].element_size()
-    print(json.dumps({"kernel_case": spec, "in_bytes": nb, "out_bytes": numel * dsts[0].element_size(),
+    total = nbatch * (nb + numel * dsts[0].element_size())
+    print(json.dumps({"kernel_case": spec, "in_bytes": nbatch * nb, "out_bytes": nbatch * numel * dsts[0].element_size(),
                       "median_ms": ms, "hbm_gbps": total / ms / 1e6}), flush=True)
 
 

@@ -191,15 +191,27 @@ static int balanced_tile_blocks(int64_t n_blocks, int64_t grid, int target, int 
     return (int)(tg * 8);
 }
 
-// Default shapes, chosen from measurements on B200 (148 SMs).
+// Default kernel shapes, chosen from sweeps on B200 (148 SMs, HBM3e).  What the
+// sweeps showed: two stages beat deeper rings (reads that run far ahead of the
+// writes cost DRAM efficiency), two or three CTAs per SM beat full occupancy,
+// and an output tile of about 32 KB per CTA is the sweet spot.
+struct Shape { int tile_blocks, stages, threads, ctas_per_sm; };
+
+static Shape default_shape(int ggml_type, int out_dtype)
+{
+    if (out_dtype == O_F32) return Shape{256, 2, 256, 2};
+    if (ggml_type == T_Q8_0) return Shape{256, 2, 256, 3};
+    return Shape{512, 2, 256, 2};
+}
+
 static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
 {
-    (void)out_dtype;
+    const Shape d = default_shape(ggml_type, out_dtype);
     if (c->variant == 0) c->variant = 1;
-    if (c->threads <= 0) c->threads = 256;
-    if (c->stages <= 0) c->stages = 4;
-    if (c->ctas_per_sm <= 0) c->ctas_per_sm = 2;
-    if (c->tile_blocks <= 0) c->tile_blocks = (ggml_type == T_Q8_0) ? 256 : 512;
+    if (c->threads <= 0) c->threads = d.threads;
+    if (c->stages <= 0) c->stages = d.stages;
+    if (c->ctas_per_sm <= 0) c->ctas_per_sm = d.ctas_per_sm;
+    if (c->tile_blocks <= 0) c->tile_blocks = d.tile_blocks;
     if (c->streaming_stores < 0) c->streaming_stores = 1;
 }
 
@@ -340,9 +352,22 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
 static int launch_batch_kernel(const pfhe_tensor_desc *d, const int *idx, int count, cudaStream_t stream, int dev, int sms,
                                const pfhe_launch_cfg *cfg)
 {
-    const int threads = cfg && cfg->threads > 0 ? cfg->threads : 256;
-    const int cps = cfg && cfg->ctas_per_sm > 0 ? cfg->ctas_per_sm : 2;
-    const int target = cfg && cfg->tile_blocks > 0 ? cfg->tile_blocks : 512;
+    // Shape of the kind that holds most of the batch's blocks.
+    int64_t weight[kMaxBatch] = {0};
+    int lead = 0;
+    for (int i = 0; i < count; ++i) {
+        for (int j = 0; j <= i; ++j) {
+            if (d[idx[j]].ggml_type == d[idx[i]].ggml_type && d[idx[j]].out_dtype == d[idx[i]].out_dtype) {
+                weight[j] += (d[idx[i]].n_elements + 31) / 32;
+                if (weight[j] > weight[lead]) lead = j;
+                break;
+            }
+        }
+    }
+    const Shape ds = default_shape(d[idx[lead]].ggml_type, d[idx[lead]].out_dtype);
+    const int threads = cfg && cfg->threads > 0 ? cfg->threads : ds.threads;
+    const int cps = cfg && cfg->ctas_per_sm > 0 ? cfg->ctas_per_sm : ds.ctas_per_sm;
+    const int target = cfg && cfg->tile_blocks > 0 ? cfg->tile_blocks : ds.tile_blocks;
     BatchKernelArgs a;
     memset(&a, 0, sizeof a);
     int64_t blocks = 0;
@@ -355,7 +380,7 @@ static int launch_batch_kernel(const pfhe_tensor_desc *d, const int *idx, int co
         blocks += a.t[i].n_blocks;
     }
     a.n_tensors = count;
-    a.stages = cfg && cfg->stages > 0 ? cfg->stages : 4;
+    a.stages = cfg && cfg->stages > 0 ? cfg->stages : ds.stages;
     int rc;
     if ((rc = status_word(dev, &a.status))) return rc;
     const int64_t max_ctas = (int64_t)sms * cps;

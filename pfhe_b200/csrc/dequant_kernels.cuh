@@ -386,10 +386,17 @@ __device__ __forceinline__ void decode_tile(const PackedTensor &pt, int64_t tb0,
     const int full_units = valid / VEC;
     uint8_t *out = reinterpret_cast<uint8_t *>(pt.dst) + e0 * OutT<OUT>::kSize;
 
+    // blockDim.x is a multiple of UPB, so a thread keeps the same position inside
+    // its block from step to step and both addresses advance by constants.
+    const int c = threadIdx.x % UPB;
+    const uint8_t *bp = tile + (threadIdx.x / UPB) * BB;
+    uint8_t *op = out + (size_t)threadIdx.x * 16;
+    const int bstep = (blockDim.x / UPB) * BB;
+    const int ostep = blockDim.x * 16;
 #pragma unroll 4
-    for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
-        const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
-        store16<kStream>(out + (size_t)u * 16, r);
+    for (int u = threadIdx.x; u < full_units; u += blockDim.x, bp += bstep, op += ostep) {
+        const uint4 r = decode_unit<T, MID, OUT, true>(bp, c);
+        store16<kStream>(op, r);
     }
     // Ragged end of the tensor (n_elements not a multiple of VEC): scalar stores.
     if (valid % VEC != 0 && threadIdx.x == 0) {
@@ -430,7 +437,10 @@ __device__ __forceinline__ bool decode_run(const PackedTensor &pt, int64_t first
     int k = 0;
     for (; k < n_tiles; ++k) {
         const int s = k % ring.stages;
-        const bool ok = mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs);
+        // One thread watches the barrier; the rest sleep in the CTA barrier instead of
+        // spinning (spinning warps take issue slots from the warps that decode).
+        bool ok = true;
+        if (threadIdx.x == 0) ok = mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs);
         // Every thread must agree before touching the tile or leaving the loop.
         if (__syncthreads_or(!ok)) break;
         ring.parity_bits ^= 1u << s;
@@ -555,7 +565,8 @@ __global__ void __launch_bounds__(512) dequant_blocks_batch(const __grid_constan
     int j = 0;
     for (; j < n_my; ++j) {
         const int s = j % ring.stages;
-        const bool ok = mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs);
+        bool ok = true;
+        if (threadIdx.x == 0) ok = mbar_wait_bounded(&ring.full[s], (ring.parity_bits >> s) & 1u, kDeviceWaitLimitNs);
         if (__syncthreads_or(!ok)) break;
         ring.parity_bits ^= 1u << s;
 

@@ -6,8 +6,10 @@
 // (src/phfe/inference/gguf_loader.py:356 and :378), which copies already
 // dequantised fp32 data from pageable memory synchronously.
 #include "common.h"
+#include "host_copy.h"
 
 #include <errno.h>
+#include <stdlib.h>
 #include <unistd.h>
 
 #include <atomic>
@@ -137,6 +139,7 @@ struct pfhe_loader {
     CopyPool *pool = nullptr;
     pfhe_loader_stats stats{};
     std::mutex mu;                       // one submit at a time per loader
+    bool streaming_copy = true;          // non-temporal stores into the pinned slots
     int slot_timeout_ms = 120000;
 };
 
@@ -158,7 +161,7 @@ int fill_pinned(pfhe_loader *ld, uint8_t *dst, const Source &src, int64_t offset
         const int64_t a = (int64_t)i * kCopyPiece;
         const int64_t n = (bytes - a) < kCopyPiece ? (bytes - a) : kCopyPiece;
         if (src.host) {
-            memcpy(dst + a, src.host + offset + a, (size_t)n);
+            copy_to_pinned(dst + a, src.host + offset + a, (size_t)n, ld->streaming_copy);
         } else {
             int64_t got = 0;
             while (got < n) {
@@ -267,6 +270,7 @@ int pfhe_loader_create(int device, int n_slots, int64_t slot_bytes, int n_thread
         unsigned hc = std::thread::hardware_concurrency();
         n_threads = hc >= 32 ? 8 : (hc >= 8 ? 4 : 2);
     }
+    if (const char *mode = getenv("PFHE_HOST_COPY")) ld->streaming_copy = strcmp(mode, "memcpy") != 0;
     ld->pool = new CopyPool(n_threads - 1);
     *out = ld;
     return PFHE_OK;

@@ -22,6 +22,7 @@ import ctypes
 import fnmatch
 import logging
 import mmap
+import os
 import struct
 from contextlib import contextmanager
 from dataclasses import dataclass, field
@@ -151,13 +152,28 @@ class _Stager:
     _by_device: Dict[int, "_Stager"] = {}
     slot_bytes = 64 << 20
     n_slots = 4
-    n_threads = 0
+    source = os.environ.get("PFHE_SOURCE", "mmap")   # "mmap": copy out of the mapping; "pread": read the file
+    n_threads = 0          # 0: from PFHE_COPY_THREADS, else half the cores this rank can claim (2..12)
+
+    @classmethod
+    def _copy_threads(cls) -> int:
+        if cls.n_threads > 0:
+            return cls.n_threads
+        env = os.environ.get("PFHE_COPY_THREADS")
+        if env:
+            return max(1, int(env))
+        try:
+            cores = len(os.sched_getaffinity(0))
+        except AttributeError:
+            cores = os.cpu_count() or 4
+        ranks_here = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1")))
+        return max(2, min(12, cores // (2 * ranks_here)))
 
     def __init__(self, device_index: int):
         self.device_index = device_index
         handle = ctypes.c_void_p()
         _native.check(_native.lib().pfhe_loader_create(device_index, self.n_slots, self.slot_bytes,
-                                                       self.n_threads, ctypes.byref(handle)))
+                                                       self._copy_threads(), ctypes.byref(handle)))
         self.handle = handle
 
     @classmethod
@@ -178,6 +194,13 @@ class _Stager:
         stream = torch.cuda.current_stream(dst.device).cuda_stream
         _native.check(_native.lib().pfhe_loader_submit(
             self.handle, host_addr, nbytes, ggml_type, mid, out,
+            dst.data_ptr(), dst.numel() * dst.element_size(), numel, stream))
+
+    def submit_fd(self, fd: int, offset: int, nbytes: int, ggml_type: int, mid: int, out: int, dst: torch.Tensor,
+                  numel: int) -> None:
+        stream = torch.cuda.current_stream(dst.device).cuda_stream
+        _native.check(_native.lib().pfhe_loader_submit_fd(
+            self.handle, fd, offset, nbytes, ggml_type, mid, out,
             dst.data_ptr(), dst.numel() * dst.element_size(), numel, stream))
 
     def wait(self, timeout_ms: int = 600000) -> None:
@@ -400,10 +423,15 @@ class GGUFReader:
                 return t32.to(device=want, dtype=dtype)
             target = torch.empty(shape, dtype=dtype, device=cuda_dev)
         if numel:
-            host = self._host_address(start, nbytes)
+            if start + nbytes > len(self._mmap):
+                raise ValueError(f"Data too short: {max(len(self._mmap) - start, 0)} < {nbytes}")
             with torch.cuda.device(cuda_dev):
-                _Stager.get(cuda_dev.index).submit(host, nbytes, info.dtype, _TORCH_TO_OUT[dtype],
-                                                   _TORCH_TO_OUT[target.dtype], target, numel)
+                stager = _Stager.get(cuda_dev.index)
+                args = (nbytes, info.dtype, _TORCH_TO_OUT[dtype], _TORCH_TO_OUT[target.dtype], target, numel)
+                if _Stager.source == "pread":
+                    stager.submit_fd(self._file.fileno(), start, *args)
+                else:   # host threads copy out of the mapping (first-touch faults happen in those threads)
+                    stager.submit(self._host_address(start, nbytes), *args)
         if out is not None:
             return out
         return target if want.type == "cuda" else target.to(want)

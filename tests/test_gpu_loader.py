@@ -166,3 +166,45 @@ def test_truncated_file_raises(tmp_path, golden_dir):
     with gl.GGUFReader(p) as r:
         with pytest.raises(ValueError, match="Data too short"):
             r.read_tensor("ragged.weight", device="cuda")
+
+
+@pytest.mark.parametrize("via", ["pointer", "fd"])
+def test_loader_c_abi_host_sources(tmp_path, via):
+    """pfhe_loader_submit / pfhe_loader_submit_fd called directly, chunked (slot smaller than the tensor)."""
+    import ctypes
+    from pfhe_b200 import _native
+    L = _native.lib()
+    numel = 32 * 40000 + 17
+    raw = synth.random_packed(gl.GGML_TYPE_Q4_0, numel, np.random.default_rng(8))
+    want = np_oracle.read_tensor(gl.GGML_TYPE_Q4_0, raw, numel, "bf16", via_dtype="f16")
+    handle = ctypes.c_void_p()
+    _native.check(L.pfhe_loader_create(torch.cuda.current_device(), 3, 100000, 3, ctypes.byref(handle)))
+    try:
+        dst = torch.zeros(numel, dtype=torch.bfloat16, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        if via == "pointer":
+            rc = L.pfhe_loader_submit(handle, raw.ctypes.data, raw.size, 2, _native.OUT_F16, _native.OUT_BF16,
+                                      dst.data_ptr(), numel * 2, numel, stream)
+        else:
+            path = tmp_path / "blob.bin"
+            path.write_bytes(b"\0" * 96 + raw.tobytes())
+            fd = os.open(path, os.O_RDONLY)
+            try:
+                rc = L.pfhe_loader_submit_fd(handle, fd, 96, raw.size, 2, _native.OUT_F16, _native.OUT_BF16,
+                                             dst.data_ptr(), numel * 2, numel, stream)
+                _native.check(rc)
+                _native.check(L.pfhe_loader_wait(handle, 60000))
+                # reading past the end of the file is an error, not a hang
+                scratch = torch.zeros(numel, dtype=torch.float16, device="cuda")
+                rc2 = L.pfhe_loader_submit_fd(handle, fd, 96 + 64, raw.size, 2, 1, 1, scratch.data_ptr(), numel * 2, numel, stream)
+                assert rc2 == _native.ERR_BAD_ARG and "pread" in _native.last_error()
+            finally:
+                os.close(fd)
+        _native.check(rc)
+        _native.check(L.pfhe_loader_wait(handle, 60000))
+        assert_same_bits(to_bits(dst), want, "bf16", via)
+        st = _native.LoaderStats()
+        _native.check(L.pfhe_loader_get_stats(handle, ctypes.byref(st)))
+        assert st.chunks >= 7 and st.bytes_staged >= raw.size
+    finally:
+        assert L.pfhe_loader_destroy(handle) == 0
