@@ -1,0 +1,117 @@
+"""Row-shard planning (CPU) and the replicated-layout all-gather over gloo with two ranks."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import np_oracle
+from pfhe_b200 import gguf_loader as gl
+from pfhe_b200 import sharding, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_row_ranges_tile_the_rows():
+    for rows in (1, 7, 8, 1024, 128256, 11008):
+        for world in (1, 2, 3, 4, 8):
+            spans = [sharding.row_range(rows, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= 1
+    with pytest.raises(ValueError):
+        sharding.row_range(8, 2, 2)
+
+
+def test_shard_bytes_decode_to_the_rows_of_the_whole(tmp_path):
+    """The byte range a rank stages holds exactly its rows: decoding it gives whole[r0:r1]."""
+    path = tmp_path / "m.gguf"
+    specs = [synth.TensorSpec("a.weight", (96, 64), gl.GGML_TYPE_Q4_1), synth.TensorSpec("b.weight", (50, 32), gl.GGML_TYPE_Q8_0),
+             synth.TensorSpec("c.weight", (10, 4, 64), gl.GGML_TYPE_Q4_0), synth.TensorSpec("n.weight", (64,), gl.GGML_TYPE_F32),
+             synth.TensorSpec("h.weight", (9, 5), gl.GGML_TYPE_F16)]
+    synth.write_gguf(path, specs, seed=4)
+    with gl.GGUFReader(path) as r:
+        for world in (1, 2, 4, 8):
+            total = 0
+            for name, info in r.tensors.items():
+                raw = np.frombuffer(r.read_tensor_raw(name), dtype=np.uint8)
+                whole = np_oracle.read_tensor(info.dtype, raw, info.numel, "f32").reshape(info.shape)
+                pieces = []
+                for rank in range(world):
+                    off, nb, ne, rows = sharding.shard_extent(info, rank, world)
+                    part = np_oracle.read_tensor(info.dtype, raw[off:off + nb], ne, "f32")
+                    if rows is None:
+                        assert (off, nb, ne) == (0, info.nbytes, info.numel)
+                        assert np.array_equal(part.view(np.uint32), whole.reshape(-1).view(np.uint32))
+                    else:
+                        assert np.array_equal(part.view(np.uint32), whole[rows[0]:rows[1]].reshape(-1).view(np.uint32))
+                        pieces.append(nb)
+                if pieces:
+                    assert sum(pieces) == info.nbytes
+                total += 1
+            b0, e0 = sharding.plan_bytes(r.tensors.values(), 0, world)
+            assert b0 > 0 and e0 > 0
+            assert list(sharding.plan(r.tensors, 0, world)) == list(r.tensors)
+    bad = gl.GGUFTensorInfo("x", 2, (48, 4), gl.GGML_TYPE_Q4_0, 0)        # row length 48 is not whole blocks
+    with pytest.raises(ValueError, match="whole 32-element blocks"):
+        sharding.shard_extent(bad, 0, 2)
+
+
+def test_70b_shape_shards_evenly():
+    specs = synth.llama_specs(synth.LLAMA3_70B)
+    infos = [gl.GGUFTensorInfo(s.name, len(s.shape), tuple(reversed(s.shape)), s.ggml_type, 0) for s in specs]
+    whole_b, whole_e = sharding.plan_bytes(infos, 0, 1)
+    assert whole_e == 68451041280 + 2101346304 + 1318912
+    per_rank = [sharding.plan_bytes(infos, r, 8) for r in range(8)]
+    assert len({p for p in per_rank}) == 1                                # every rank reads the same amount
+    small = sum(i.nbytes for i in infos if len(i.shape) < 2)
+    assert per_rank[0][0] == (whole_b - small) // 8 + small
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _gather_worker(rank, world, port, rows, cols, q):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from pfhe_b200 import sharding as sh
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(1)
+        whole = torch.randn(rows, cols, generator=g).to(torch.bfloat16)
+        full = torch.zeros(rows, cols, dtype=torch.bfloat16)
+        r0, r1 = sh.row_range(rows, rank, world)
+        full[r0:r1] = whole[r0:r1]                      # what this rank "decoded"
+        sh.all_gather_rows(full, None)
+        sub = dist.new_group(list(range(world)))
+        full2 = torch.zeros(rows, cols, dtype=torch.bfloat16)
+        full2[r0:r1] = whole[r0:r1]
+        sh.all_gather_rows(full2, sub)
+        q.put((rank, bool(torch.equal(full, whole)) and bool(torch.equal(full2, whole))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rows", [8, 7])      # even shares (one all_gather) and ragged shares (broadcasts)
+def test_all_gather_rows_gloo_two_ranks(rows):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, rows, 16, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(results) == [(0, True), (1, True)]
