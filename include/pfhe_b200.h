@@ -140,6 +140,45 @@ int pfhe_dequant_launch_batch_ex(const pfhe_tensor_desc *tensors, int n_tensors,
                                  const pfhe_launch_cfg *cfg);
 
 /*
+ * Decode one tensor whose packed bytes are in host memory WITHOUT allocating
+ * anything, on the device or on the host.  (No counterpart in the reference,
+ * which allocates freely; this is for embedders that cannot.)
+ *
+ * Who needs it: a serving process that gives all device memory to its own pool
+ * at start-up, so that a later cudaMalloc fails or stalls the device while it
+ * synchronises; a latency-critical loop that forbids allocation after warm-up.
+ * Every other host-source entry point of this library allocates on first use
+ * (staging slots, a pinned status word).
+ *
+ * How: the packed bytes are copied with cudaMemcpyAsync into a scratch array
+ * that is part of the library image (a static __device__ array of
+ * 256 + PFHE_NOALLOC_MAX_PACKED_BYTES bytes, held by every GPU that loads the
+ * library until the process exits) and decoded from there by the same kernels
+ * as pfhe_dequant_launch; results are bit-identical to it.  The memset, copy
+ * and kernel are queued on `stream` in that order.
+ *
+ * Limits and rules:
+ *  - ceil(n_elements/block) * block_bytes must not exceed
+ *    PFHE_NOALLOC_MAX_PACKED_BYTES (8 MiB); larger tensors are rejected with
+ *    PFHE_ERR_BAD_ARG and a message -- decode them as row slices.
+ *  - The first call on a device looks up the scratch's device address
+ *    (cudaGetSymbolAddress) with that device current; make that first call
+ *    before any stream capture begins.
+ *  - All calls on a device share the one scratch array.  Calls on the same
+ *    stream are ordered and safe; calls whose GPU work can overlap (different
+ *    streams without an event between them, or several threads) race on it.
+ *  - host_src must stay valid until the copy has run (as for any
+ *    cudaMemcpyAsync; pageable memory is copied before the call returns).
+ *  - A device-side wait failure is recorded in the scratch header, which the
+ *    next call clears; it is not reported through pfhe_device_status.
+ */
+#define PFHE_NOALLOC_MAX_PACKED_BYTES (8 * 1024 * 1024)
+int pfhe_dequant_from_host_noalloc(int ggml_type, int out_dtype,
+                                   const void *host_src, int64_t src_bytes,
+                                   void *dst_dev, int64_t dst_bytes,
+                                   int64_t n_elements, void *stream);
+
+/*
  * Reads and clears the device-side wait status of `device` (-1 = current).
  * A decode kernel that gave up waiting for one of its bulk copies records
  * PFHE_ERR_DEVICE_WAIT here and returns without hanging.  Call after

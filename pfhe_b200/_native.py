@@ -19,11 +19,13 @@ ERR_BAD_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_DEVICE_WAIT = -5, -6, -7, -8
 # enum pfhe_out_dtype
 OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
 
+NOALLOC_MAX_PACKED_BYTES = 8 * 1024 * 1024   # PFHE_NOALLOC_MAX_PACKED_BYTES
+
 # Every symbol include/pfhe_b200.h declares.
 EXPORTED_SYMBOLS = (
     "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes",
     "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex", "pfhe_dequant_launch_batch", "pfhe_dequant_launch_batch_ex",
-    "pfhe_device_status", "pfhe_launch_count",
+    "pfhe_dequant_from_host_noalloc", "pfhe_device_status", "pfhe_launch_count",
     "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd",
     "pfhe_loader_wait", "pfhe_loader_get_stats", "pfhe_loader_destroy",
 )
@@ -75,6 +77,8 @@ def lib() -> ctypes.CDLL:
     L.pfhe_dequant_launch_batch.argtypes = [ctypes.POINTER(TensorDesc), i32, vp]
     L.pfhe_dequant_launch_batch_ex.restype = i32
     L.pfhe_dequant_launch_batch_ex.argtypes = [ctypes.POINTER(TensorDesc), i32, vp, ctypes.POINTER(LaunchCfg)]
+    L.pfhe_dequant_from_host_noalloc.restype = i32
+    L.pfhe_dequant_from_host_noalloc.argtypes = [i32, i32, vp, i64, vp, i64, i64, vp]
     L.pfhe_device_status.restype = i32
     L.pfhe_device_status.argtypes = [i32]
     L.pfhe_launch_count.restype = i64

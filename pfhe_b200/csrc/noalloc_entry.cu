@@ -1,0 +1,165 @@
+// pfhe_dequant_from_host_noalloc: host bytes -> device -> decode, allocating nothing.
+//
+// For callers that cannot allocate device memory when they need a tensor
+// decoded: serving processes that hand every byte of HBM to their own pool at
+// start-up (so a later cudaMalloc fails or stalls the whole device while it
+// synchronises), and latency-critical loops whose rules forbid allocation after
+// warm-up.  The ordinary path needs device staging memory and a pinned status
+// word, which it allocates on first use; this entry point keeps both in one
+// file-scope device array that every GPU holds from the moment the library is
+// loaded until the process exits.
+#include "common.h"
+#include "dequant_kernels.cuh"
+
+#include <atomic>
+#include <mutex>
+
+namespace pfhe {
+extern std::atomic<int64_t> g_launch_count;   // defined beside pfhe_launch_count()
+}
+
+namespace {
+
+using namespace pfhe;
+
+constexpr size_t kHeaderBytes = 256;                           // status word, cleared by every call
+constexpr size_t kMaxPacked = PFHE_NOALLOC_MAX_PACKED_BYTES;   // staged packed bytes
+
+// Scratch shared by every call on a device.  In host code this name is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kHeaderBytes + kMaxPacked];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_setup_mu;
+unsigned char *g_scratch_addr[kMaxDevices];                    // per device, set once
+int g_sm_count[kMaxDevices];
+
+// First call on a device (with that device current): look up where the array
+// lives on it and how many SMs it has.
+int setup_device(int dev, unsigned char **scratch, int *sms)
+{
+    std::lock_guard<std::mutex> lk(g_setup_mu);
+    if (!g_scratch_addr[dev]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(no-alloc scratch)");
+        if (!p) { set_error("no-alloc scratch has no device address"); return PFHE_ERR_CUDA; }
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        g_sm_count[dev] = n;
+        g_scratch_addr[dev] = static_cast<unsigned char *>(p);
+    }
+    *scratch = g_scratch_addr[dev];
+    *sms = g_sm_count[dev];
+    return PFHE_OK;
+}
+
+template <int T, int OUT>
+void launch_blocks(const uint8_t *src, void *dst, int64_t n, int *status, int sms, cudaStream_t stream)
+{
+    BlockKernelArgs a;
+    a.t.src16 = src;                                           // the scratch is 256-byte aligned: no skew
+    a.t.skew = 0;
+    a.t.dst = dst;
+    a.t.n_elements = n;
+    a.t.n_blocks = (n + 31) / 32;
+    a.t.span_bytes = (a.t.n_blocks * Fmt<T>::kBytes + 15) & ~(int64_t)15;
+    a.t.kind = 0;
+    a.stages = 2;
+    a.interleaved = 1;
+    a.status = status;
+    const int64_t n_groups = (a.t.n_blocks + 7) / 8;
+    const int64_t max_ctas = (int64_t)sms * 2;
+    const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
+    const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
+    const int target = OUT == O_F32 ? 256 : 512;               // 34.8 KB of shared memory at most: no opt-in needed
+    a.tile_blocks = groups_per_cta * 8 < target ? (int)(groups_per_cta * 8) : target;
+    const size_t smem = (size_t)a.stages * (a.tile_blocks * Fmt<T>::kBytes + 16);
+    dequant_blocks_staged<T, OUT, OUT, true><<<(unsigned)grid, 256, smem, stream>>>(a);
+}
+
+template <int T, int OUT>
+void launch_elements(const uint8_t *src, void *dst, int64_t n, int sms, cudaStream_t stream)
+{
+    constexpr int wide = Fmt<T>::kBytes > OutT<OUT>::kSize ? Fmt<T>::kBytes : OutT<OUT>::kSize;
+    int64_t blocks = (n / (16 / wide) + 1023) / 1024;
+    if (blocks < 1) blocks = 1;
+    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    convert_elements<T, OUT, OUT, true><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n);
+}
+
+template <int T, int OUT>
+void launch_any(const uint8_t *src, void *dst, int64_t n, int sms, cudaStream_t stream)
+{
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
+    dequant_any_alignment<T, OUT, OUT><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n);
+}
+
+template <int T>
+void dispatch_out(int out, const uint8_t *src, void *dst, int64_t n, int *status, int sms, cudaStream_t stream)
+{
+    const bool aligned = reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+#define PFHE_GO(O)                                                                   \
+    if (!aligned) launch_any<T, O>(src, dst, n, sms, stream);                        \
+    else if constexpr (Fmt<T>::kElems == 32) launch_blocks<T, O>(src, dst, n, status, sms, stream); \
+    else launch_elements<T, O>(src, dst, n, sms, stream);
+    if (out == O_F32) { PFHE_GO(O_F32) }
+    else if (out == O_F16) { PFHE_GO(O_F16) }
+    else { PFHE_GO(O_BF16) }
+#undef PFHE_GO
+}
+
+}  // namespace
+
+extern "C" int pfhe_dequant_from_host_noalloc(int ggml_type, int out_dtype, const void *host_src, int64_t src_bytes,
+                                              void *dst_dev, int64_t dst_bytes, int64_t n_elements, void *stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int be = 0, bb = 0;
+    int rc = type_geometry(ggml_type, &be, &bb);
+    if (rc) return rc;
+    const int osz = out_size(out_dtype);
+    if (osz == 0) { set_error("output dtype %d not in {f32,f16,bf16}", out_dtype); return PFHE_ERR_BAD_DTYPE; }
+    if (n_elements < 0 || src_bytes < 0 || dst_bytes < 0) { set_error("negative size"); return PFHE_ERR_BAD_ARG; }
+    const int64_t need = (n_elements + be - 1) / be * bb;
+    if (src_bytes < need) { set_error("Data too short: %lld < %lld", (long long)src_bytes, (long long)need); return PFHE_ERR_SHORT_SOURCE; }
+    if (dst_bytes < n_elements * osz) { set_error("destination too small: %lld < %lld", (long long)dst_bytes, (long long)(n_elements * osz)); return PFHE_ERR_SHORT_DEST; }
+    if ((uint64_t)need > kMaxPacked) {
+        set_error("pfhe_dequant_from_host_noalloc stages at most %lld packed bytes per call; this tensor needs %lld "
+                  "(split it into row slices, or use the pfhe_loader_* entry points)",
+                  (long long)kMaxPacked, (long long)need);
+        return PFHE_ERR_BAD_ARG;
+    }
+    if (n_elements == 0) return PFHE_OK;
+    if (!host_src || !dst_dev) { set_error("null pointer"); return PFHE_ERR_BAD_ARG; }
+    if (reinterpret_cast<uintptr_t>(dst_dev) % osz) { set_error("destination not aligned to its element size"); return PFHE_ERR_BAD_ARG; }
+
+    int dev = 0, sms = 0;
+    if ((rc = current_device(&dev))) return rc;
+    unsigned char *scratch = nullptr;
+    if ((rc = setup_device(dev, &scratch, &sms))) return rc;
+
+    // The array still holds whatever the previous call left: the status word must
+    // start at zero, the staged bytes are overwritten by the copy.
+    cudaError_t e = cudaMemsetAsync(scratch, 0, kHeaderBytes, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(no-alloc status)");
+    e = cudaMemcpyAsync(scratch + kHeaderBytes, host_src, (size_t)need, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(no-alloc staging)");
+
+    const uint8_t *src = scratch + kHeaderBytes;
+    int *status = reinterpret_cast<int *>(scratch);
+    switch (ggml_type) {
+    case T_Q4_0: dispatch_out<T_Q4_0>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q4_1: dispatch_out<T_Q4_1>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q8_0: dispatch_out<T_Q8_0>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_F16: dispatch_out<T_F16>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_BF16: dispatch_out<T_BF16>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    default: dispatch_out<T_F32>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "no-alloc decode launch");
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return PFHE_OK;
+}

@@ -1,0 +1,95 @@
+"""The entry point for callers that cannot allocate: pfhe_dequant_from_host_noalloc.
+
+Some embedders of this library may not allocate when they need a tensor
+decoded -- a serving process whose own pool already owns all device memory, or
+a loop that forbids allocation after warm-up.  The entry point stages the
+packed bytes in a scratch array that is part of the library image, so it calls
+no allocator at all.  This file checks, through the C ABI, that it produces
+exactly what the ordinary entry point produces, on two calls in a row (the
+scratch keeps the previous call's contents, so the second call must not see
+them), and that it refuses tensors beyond its stated limit.
+
+The file name sorts last on purpose: a run that stops at the first failure has
+then already run every other test.  The test does not depend on that order.
+"""
+import numpy as np
+import pytest
+import torch
+
+from pfhe_b200 import _native, synth
+
+pytestmark = pytest.mark.gpu
+
+OUT = {"f32": (_native.OUT_F32, torch.float32), "f16": (_native.OUT_F16, torch.float16),
+       "bf16": (_native.OUT_BF16, torch.bfloat16)}
+TYPES = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8, "F16": 1, "BF16": 30, "F32": 0}
+
+
+def _bits(t):
+    t = t.reshape(-1).cpu()
+    return t.view(torch.int32 if t.dtype == torch.float32 else torch.int16)
+
+
+def _existing_entry_point(ggml_type, raw, numel, out):
+    """pfhe_dequant_launch on a device copy of the packed bytes."""
+    L = _native.lib()
+    oid, odt = OUT[out]
+    src = torch.from_numpy(raw).cuda()
+    dst = torch.empty(numel, dtype=odt, device="cuda")
+    _native.check(L.pfhe_dequant_launch(ggml_type, oid, src.data_ptr(), src.numel(), dst.data_ptr(),
+                                        numel * dst.element_size(), numel, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return dst
+
+
+def _no_alloc_entry_point(ggml_type, raw, numel, dst):
+    L = _native.lib()
+    oid = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dst.dtype]
+    return L.pfhe_dequant_from_host_noalloc(ggml_type, oid, raw.ctypes.data, raw.size, dst.data_ptr(),
+                                            numel * dst.element_size(), numel, torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("fmt", list(TYPES))
+@pytest.mark.parametrize("out", list(OUT))
+def test_two_calls_in_a_row_match_the_existing_entry_point(fmt, out):
+    t = TYPES[fmt]
+    # second call is shorter than the first and has other contents: stale scratch bytes would show
+    cases = [(32 * 5000 + 13, 1), (32 * 777, 2)]
+    dsts = [torch.zeros(n, dtype=OUT[out][1], device="cuda") for n, _ in cases]   # allocated before the calls
+    raws = [np.ascontiguousarray(synth.random_packed(t, n, np.random.default_rng(seed))) for n, seed in cases]
+    for (n, _), raw, dst in zip(cases, raws, dsts):                              # two calls back to back, one stream
+        _native.check(_no_alloc_entry_point(t, raw, n, dst))
+    torch.cuda.synchronize()
+    for (n, _), raw, dst in zip(cases, raws, dsts):
+        want = _existing_entry_point(t, raw, n, out)
+        assert torch.equal(_bits(dst), _bits(want)), f"{fmt}->{out}, {n} elements"   # bit-exact, as everywhere in this suite
+
+
+def test_largest_accepted_and_first_rejected_size():
+    limit = _native.NOALLOC_MAX_PACKED_BYTES
+    numel_ok = limit // 34 * 32                       # Q8_0: 34 bytes per 32 elements
+    raw = np.ascontiguousarray(synth.random_packed(8, numel_ok, np.random.default_rng(3)))
+    dst = torch.zeros(numel_ok, dtype=torch.float16, device="cuda")
+    _native.check(_no_alloc_entry_point(8, raw, numel_ok, dst))
+    torch.cuda.synchronize()
+    assert torch.equal(_bits(dst), _bits(_existing_entry_point(8, raw, numel_ok, "f16")))
+
+    numel_big = numel_ok + 32
+    raw_big = np.zeros(numel_big // 32 * 34, dtype=np.uint8)
+    dst_big = torch.full((numel_big,), 7.0, dtype=torch.float16, device="cuda")
+    rc = _no_alloc_entry_point(8, raw_big, numel_big, dst_big)
+    assert rc == _native.ERR_BAD_ARG
+    assert "at most" in _native.last_error() and str(limit) in _native.last_error()
+    torch.cuda.synchronize()
+    assert bool((dst_big == 7.0).all())               # nothing was queued
+
+
+def test_argument_errors():
+    dst = torch.zeros(64, dtype=torch.float16, device="cuda")
+    raw = np.zeros(36, dtype=np.uint8)
+    assert _no_alloc_entry_point(12, raw, 32, dst) == _native.ERR_BAD_TYPE
+    assert _no_alloc_entry_point(2, raw[:17], 32, dst) == _native.ERR_SHORT_SOURCE
+    L = _native.lib()
+    assert L.pfhe_dequant_from_host_noalloc(2, 1, raw.ctypes.data, 36, dst.data_ptr(), 10, 32, None) == _native.ERR_SHORT_DEST
+    assert L.pfhe_dequant_from_host_noalloc(2, 1, None, 36, dst.data_ptr(), 128, 32, None) == _native.ERR_BAD_ARG
+    assert L.pfhe_dequant_from_host_noalloc(2, 1, raw.ctypes.data, 36, dst.data_ptr(), 128, 0, None) == _native.OK
