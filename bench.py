@@ -299,6 +299,13 @@ def run_gpu_arm(args) -> None:
     e2e = run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch)
     clocks = sampler.stop() if rank == 0 else None
 
+    # --- whole-model loads (after the timed legs; needs the HBM the batch buffers hold) ----------
+    model_load = None
+    if not args.no_model_load:
+        del srcs, dsts, descs
+        torch.cuda.empty_cache()
+        model_load = run_model_loads(args, rank, world, dev, torch, dist)
+
     # --- max over ranks -------------------------------------------------------------------
     t = torch.tensor([total_ms, e2e["ms_per_step"]], dtype=torch.float64, device=dev)
     if world > 1:
@@ -342,10 +349,182 @@ def run_gpu_arm(args) -> None:
         }
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
+        if model_load is not None:
+            line["model_load"] = model_load
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# Whole-model loads (reported beside the headline metric)
+# ---------------------------------------------------------------------------------------------
+def _module_tree(torch, shapes, dtype, device):
+    """A bare module whose named_parameters() are exactly the dotted GGUF names."""
+    root = torch.nn.Module()
+    for name, shape in shapes.items():
+        parts = name.split(".")
+        node = root
+        for p in parts[:-1]:
+            if p not in node._modules:
+                node.add_module(p, torch.nn.Module())
+            node = node._modules[p]
+        node.register_parameter(parts[-1], torch.nn.Parameter(torch.empty(shape, dtype=dtype, device=device),
+                                                               requires_grad=False))
+    return root
+
+
+def _shm_room(need_bytes: int):
+    base = "/dev/shm"
+    if not (os.path.isdir(base) and os.access(base, os.W_OK)):
+        return None, "no writable /dev/shm"
+    st = os.statvfs(base)
+    free = st.f_bavail * st.f_frsize
+    avail = None
+    try:
+        with open("/proc/meminfo") as f:
+            for ln in f:
+                if ln.startswith("MemAvailable:"):
+                    avail = int(ln.split()[1]) * 1024
+    except OSError:
+        pass
+    if free < need_bytes * 1.05:
+        return None, f"/dev/shm has {free / 1e9:.0f} GB free, file needs {need_bytes / 1e9:.0f} GB"
+    if avail is not None and avail < need_bytes + 24e9:
+        return None, f"host has {avail / 1e9:.0f} GB available, file needs {need_bytes / 1e9:.0f} GB"
+    return base, None
+
+
+def run_model_loads(args, rank, world, dev, torch, dist):
+    """Config 3 (7B-shaped file, streaming_dequant_context, N=1 only) and config 4 (70B-shaped
+    file, GGUFModelPatcher into row-sharded bf16 parameters, every N)."""
+    import pfhe_b200
+    from pfhe_b200 import gguf_loader as gl, sharding, synth
+
+    out = {}
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def agree(value):
+        box = [value]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def make_file(shape, tag):
+        specs, meta = synth.llama_specs(shape), synth.llama_metadata(shape)
+        need = sum(synth._align(s.nbytes) for s in specs) + (1 << 20)
+        base, why = _shm_room(need) if rank == 0 else (None, None)
+        base, why = agree((base, why))
+        if base is None:
+            return None, specs, why, 0.0
+        path = agree(os.path.join(base, f"pfhe_bench_{tag}_{os.getpid()}.gguf") if rank == 0 else None)
+        t0 = time.perf_counter()
+        if rank == 0:
+            synth.write_gguf_tiled(path, specs, meta, seed=11, part=(0, world), phase="header")
+        barrier()
+        synth.write_gguf_tiled(path, specs, meta, seed=11, part=(rank, world), threads=max(2, 12 // world), phase="tensors")
+        barrier()
+        return path, specs, None, time.perf_counter() - t0
+
+    # --- config 4: 70B-shaped, Q4_1 linears, bf16 out, row-sharded across the ranks -------------
+    path = None
+    try:
+        path, specs, why, gen_s = make_file(synth.LLAMA3_70B, "70b")
+        if path is None:
+            out["llama3_70b_q4_1_to_bf16"] = {"skipped": why}
+        else:
+            shapes = {}
+            for sp in specs:
+                if len(sp.shape) >= 2:
+                    r0, r1 = sharding.row_range(sp.shape[0], rank, world)
+                    shapes[sp.name] = (r1 - r0,) + tuple(sp.shape[1:])
+                else:
+                    shapes[sp.name] = tuple(sp.shape)
+            model = _module_tree(torch, shapes, torch.bfloat16, dev)
+            out_bytes = sum(p.numel() * 2 for p in model.parameters())
+            times = []
+            for _ in range(2):
+                barrier()
+                t0 = time.perf_counter()
+                with pfhe_b200.GGUFModelPatcher(path).patch_context(model, device=str(dev), dtype=torch.bfloat16,
+                                                                   shard=(rank, world)) as stats:
+                    pass
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+                assert stats["loaded"] == len(specs) and not stats["missing"], stats
+                t = torch.tensor([dt], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                times.append(float(t[0]))
+            with gl.GGUFReader(path) as r:
+                in_bytes, _ = sharding.plan_bytes(r.tensors.values(), rank, world)
+                file_bytes = os.path.getsize(path)
+                n_blocks = sum(-(-t_.numel // 32) for t_ in r.tensors.values() if t_.dtype in (2, 3, 8))
+            best = min(times)
+            out["llama3_70b_q4_1_to_bf16"] = {
+                "api": "GGUFModelPatcher.patch_context(dtype=bfloat16, shard=(rank, world))", "n_gpus": world,
+                "load_seconds": best, "load_seconds_each": times, "file_gb": file_bytes / 1e9,
+                "packed_gb_per_gpu": in_bytes / 1e9, "decoded_gb_per_gpu": out_bytes / 1e9,
+                "h2d_gbps_per_gpu": in_bytes / best / 1e9, "decoded_gbps_total": out_bytes * world / best / 1e9,
+                "page_cache": "warm (file in tmpfs)", "file_generation_seconds": gen_s,
+                "contents": "seeded random 4Mi-element tile per tensor, repeated to length",
+                "cpu_reference_extrapolated_hours": n_blocks * 10e-6 / 3600,
+                "cpu_reference_note": "per-block Python loop at the ~10 us/block measured by the cpu_baseline leg, single thread",
+            }
+            del model
+            torch.cuda.empty_cache()
+    except Exception as e:                       # keep the headline line even if this leg cannot run
+        out["llama3_70b_q4_1_to_bf16"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    finally:
+        barrier()
+        if path and rank == 0:
+            try:
+                os.unlink(path)
+            except OSError:
+                pass
+
+    # --- config 3: 7B-shaped, Q4_0 linears, streamed in batches of 8 into fp16, one GPU ---------
+    if world == 1:
+        path = None
+        try:
+            path, specs, why, gen_s = make_file(synth.LLAMA2_7B, "7b")
+            if path is None:
+                out["llama2_7b_q4_0_to_fp16"] = {"skipped": why}
+            else:
+                times = []
+                for _ in range(2):
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                    n_t, n_b = 0, 0
+                    with pfhe_b200.streaming_dequant_context(path, batch_size=8, device=str(dev), dtype=torch.float16) as stream:
+                        for batch_ in stream.iter_batches():
+                            n_t += len(batch_)
+                            n_b += sum(t_.numel() * 2 for t_ in batch_.values())
+                    torch.cuda.synchronize()
+                    times.append(time.perf_counter() - t0)
+                    assert n_t == len(specs)
+                best = min(times)
+                out["llama2_7b_q4_0_to_fp16"] = {
+                    "api": "streaming_dequant_context(batch_size=8, dtype=float16).iter_batches()", "n_gpus": 1,
+                    "load_seconds": best, "load_seconds_each": times, "file_gb": os.path.getsize(path) / 1e9,
+                    "decoded_gb": n_b / 1e9, "h2d_gbps": os.path.getsize(path) / best / 1e9,
+                    "page_cache": "warm (file in tmpfs)", "file_generation_seconds": gen_s,
+                }
+        except Exception as e:
+            out["llama2_7b_q4_0_to_fp16"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        finally:
+            if path:
+                try:
+                    os.unlink(path)
+                except OSError:
+                    pass
+    return out
+
 
 
 def run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch):
@@ -449,6 +628,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=16, help="tensors per step")
     ap.add_argument("--traffic-bytes", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture (profiles/), echoed into the roofline object")
+    ap.add_argument("--no-model-load", action="store_true",
+                    help="skip the whole-model load legs (7B-shaped streaming, 70B-shaped sharded patch)")
     ap.add_argument("--kernel-case", default=None,
                     help="FORMAT:OUT:NUMEL[:LAUNCHES] -- run only a few launches of one kernel (for profilers)")
     args = ap.parse_args()

@@ -233,3 +233,52 @@ def llama_metadata(m: LlamaShape, n_layers: Optional[int] = None) -> List[Tuple[
 
 def write_llama_gguf(path, m: LlamaShape, n_layers: Optional[int] = None, seed: int = 0) -> int:
     return write_gguf(path, llama_specs(m, n_layers), llama_metadata(m, n_layers), seed=seed)
+
+
+# ---------------------------------------------------------------------------
+# Fast writer for multi-gigabyte benchmark files
+# ---------------------------------------------------------------------------
+def write_gguf_tiled(path, specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str, Any]] = (), seed: int = 0,
+                     part: Tuple[int, int] = (0, 1), threads: int = 8, tile_elems: int = 1 << 22,
+                     phase: str = "all") -> int:
+    """Writes (a share of) a large GGUF file quickly; returns the full file size.
+
+    Every tensor is filled with a seeded random tile of ``tile_elems`` elements
+    (its own seed, the distributions of ``random_packed``) repeated to length,
+    which keeps generation at memory-copy speed.  ``part=(i, n)``: this caller
+    writes the header (i == 0) and the tensors whose index is ``i`` modulo ``n``;
+    ``n`` cooperating processes produce the whole file with ``pwrite``.
+    ``phase``: "all", or "header" (size the file and write the header only) followed,
+    after a barrier between the processes, by "tensors" in every process.
+    """
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    head, offsets = header_bytes(specs, metadata)
+    data_start = _align(len(head))
+    total = data_start + (offsets[-1] + specs[-1].nbytes if specs else 0)
+    who, n_parts = part
+    fd = os.open(path, os.O_RDWR | os.O_CREAT, 0o644)
+    try:
+        if who == 0 and phase in ("all", "header"):
+            os.ftruncate(fd, total)
+            os.pwrite(fd, head + b"\0" * (data_start - len(head)), 0)
+
+        def fill(i: int) -> None:
+            sp = specs[i]
+            per_block, block_bytes = QUANT_INFO[sp.ggml_type]
+            t_elems = min(max(tile_elems // per_block * per_block, per_block), -(-sp.numel // per_block) * per_block)
+            tile = random_packed(sp.ggml_type, t_elems, np.random.default_rng([seed, i]))
+            view = memoryview(np.ascontiguousarray(tile))            # written as is, no copies
+            pos, end = data_start + offsets[i], data_start + offsets[i] + sp.nbytes
+            while pos < end:
+                n = min(len(view), end - pos)
+                os.pwrite(fd, view[:n], pos)
+                pos += n
+
+        mine = [i for i in range(len(specs)) if i % n_parts == who] if phase in ("all", "tensors") else []
+        with ThreadPoolExecutor(max_workers=max(1, threads)) as pool:
+            list(pool.map(fill, mine))
+    finally:
+        os.close(fd)
+    return total

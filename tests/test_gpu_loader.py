@@ -208,3 +208,36 @@ def test_loader_c_abi_host_sources(tmp_path, via):
         assert st.chunks >= 7 and st.bytes_staged >= raw.size
     finally:
         assert L.pfhe_loader_destroy(handle) == 0
+
+
+def test_llama70b_shaped_layer_row_sharded_eight_ways(tmp_path_factory):
+    """The 70B-shaped configuration at full tensor sizes (one layer + embeddings, 3 GB packed):
+    eight row shards decoded one after another tile the whole-tensor decode, and whole tensors
+    match the C oracle."""
+    from oracle import c_oracle
+    from pfhe_b200 import sharding
+    base = "/dev/shm" if os.access("/dev/shm", os.W_OK) else str(tmp_path_factory.mktemp("big"))
+    path = os.path.join(base, f"pfhe_test_70b_{os.getpid()}.gguf")
+    specs = synth.llama_specs(synth.LLAMA3_70B, 1)
+    try:
+        synth.write_gguf_tiled(path, specs, synth.llama_metadata(synth.LLAMA3_70B, 1), seed=21, threads=8)
+        with gl.GGUFReader(path) as r:
+            assert r.tensors["blk.0.ffn_gate.weight"].shape == (28672, 8192)
+            assert r.tensors["token_embd.weight"].nbytes == 128256 * 8192 // 32 * 34
+            for name in ("blk.0.attn_k.weight", "blk.0.ffn_down.weight", "blk.0.attn_norm.weight"):
+                info = r.tensors[name]
+                whole = r.read_tensor(name, device="cuda", dtype=torch.bfloat16)
+                want = c_oracle.read_tensor(info.dtype, np.frombuffer(r.read_tensor_raw(name), dtype=np.uint8), info.numel,
+                                            "bf16", n_threads=8)
+                assert_same_bits(to_bits(whole), want, "bf16", name)
+            for name in ("token_embd.weight", "blk.0.ffn_up.weight", "blk.0.attn_q.weight"):
+                info = r.tensors[name]
+                whole = r.read_tensor(name, device="cuda", dtype=torch.bfloat16)
+                for rank in range(8):
+                    r0, r1 = sharding.row_range(info.shape[0], rank, 8)
+                    part = r.read_tensor(name, device="cuda", dtype=torch.bfloat16, rows=(r0, r1))
+                    assert torch.equal(part.view(torch.int16), whole[r0:r1].view(torch.int16)), (name, rank)
+                del whole
+    finally:
+        if os.path.exists(path):
+            os.unlink(path)
