@@ -448,14 +448,18 @@ def run_model_loads(args, rank, world, dev, torch, dist):
             model = _module_tree(torch, shapes, torch.bfloat16, dev)
             out_bytes = sum(p.numel() * 2 for p in model.parameters())
             times = []
+            stager = gl._Stager.get(dev.index)
             for _ in range(2):
+                gl.wait_for_deferred_unmaps()      # the previous load's mapping is torn down in the background
                 barrier()
+                st0 = stager.stats()
                 t0 = time.perf_counter()
                 with pfhe_b200.GGUFModelPatcher(path).patch_context(model, device=str(dev), dtype=torch.bfloat16,
                                                                    shard=(rank, world)) as stats:
-                    pass
+                    t_submitted = time.perf_counter() - t0
                 torch.cuda.synchronize()
                 dt = time.perf_counter() - t0
+                st1 = stager.stats()
                 assert stats["loaded"] == len(specs) and not stats["missing"], stats
                 t = torch.tensor([dt], dtype=torch.float64, device=dev)
                 if world > 1:
@@ -472,6 +476,9 @@ def run_model_loads(args, rank, world, dev, torch, dist):
                 "packed_gb_per_gpu": in_bytes / 1e9, "decoded_gb_per_gpu": out_bytes / 1e9,
                 "h2d_gbps_per_gpu": in_bytes / best / 1e9, "decoded_gbps_total": out_bytes * world / best / 1e9,
                 "page_cache": "warm (file in tmpfs)", "file_generation_seconds": gen_s,
+                "rank0_last_load": {"submit_seconds": t_submitted, "host_copy_seconds": st1["host_copy_seconds"] - st0["host_copy_seconds"],
+                                    "slot_wait_seconds": st1["slot_wait_seconds"] - st0["slot_wait_seconds"],
+                                    "chunks": st1["chunks"] - st0["chunks"], "copy_threads": gl._Stager._copy_threads()},
                 "contents": "seeded random 4Mi-element tile per tensor, repeated to length",
                 "cpu_reference_extrapolated_hours": n_blocks * 10e-6 / 3600,
                 "cpu_reference_note": "per-block Python loop at the ~10 us/block measured by the cpu_baseline leg, single thread",
@@ -498,6 +505,7 @@ def run_model_loads(args, rank, world, dev, torch, dist):
             else:
                 times = []
                 for _ in range(2):
+                    gl.wait_for_deferred_unmaps()
                     torch.cuda.synchronize()
                     t0 = time.perf_counter()
                     n_t, n_b = 0, 0
@@ -619,6 +627,66 @@ def run_kernel_case(spec: str) -> None:
                       "median_ms": ms, "hbm_gbps": total / ms / 1e6}), flush=True)
 
 
+def run_sweep(args) -> None:
+    """Kernel-roofline sweep: one tensor per launch, packed input 64 KB ... 2 GB, six formats,
+    fp16 and bf16 out, row lengths 4096 / 8192 / 14336, device-resident input.  One JSON line per
+    case.  Cases whose input + output stay under 256 MB are rotated over enough buffers to exceed
+    the 126 MB L2 where that takes at most 64 buffers; smaller ones are marked l2_resident."""
+    import torch
+    from pfhe_b200 import _native, synth
+    L = _native.lib()
+    peak, _ = measured_peaks()
+    fmts = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8, "F16": 1, "BF16": 30, "F32": 0}
+    outs = {"f16": (_native.OUT_F16, torch.float16), "bf16": (_native.OUT_BF16, torch.bfloat16)}
+    sizes = [64 << 10, 1 << 20, 16 << 20, 64 << 20, 256 << 20, 1 << 30, 2 << 30]
+    row_lens = [4096, 8192, 14336]
+    st = torch.cuda.current_stream()
+    rng = np.random.default_rng(5)
+    for fname, t in fmts.items():
+        tile_host = synth.random_packed(t, 1 << 20, rng)
+        tile = torch.from_numpy(tile_host).cuda()
+        for si, target in enumerate(sizes):
+            if target > args.sweep_max_bytes:
+                continue
+            K = row_lens[si % len(row_lens)]
+            row_bytes = L.pfhe_tensor_nbytes(t, K)
+            rows = max(1, target // row_bytes)
+            numel = rows * K
+            nb = rows * row_bytes
+            for oname, (oid, odt) in outs.items():
+                per = nb + numel * 2
+                nbuf = 2 if per >= (256 << 20) else min(64, -(-(300 << 20) // per))
+                resident = nbuf * per < (200 << 20)
+                srcs = [tile.repeat(-(-nb // tile.numel()))[:nb].contiguous() for _ in range(nbuf)]
+                dsts = [torch.empty(numel, dtype=odt, device="cuda") for _ in range(nbuf)]
+                def run(i):
+                    rc = L.pfhe_dequant_launch(t, oid, srcs[i % nbuf].data_ptr(), nb, dsts[i % nbuf].data_ptr(), numel * 2,
+                                               numel, st.cuda_stream)
+                    if rc:
+                        _native.check(rc)
+                iters = max(4, min(200, int(2e9 // per)))
+                for i in range(3):
+                    run(i)
+                torch.cuda.synchronize()
+                best = None
+                for _ in range(3):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(st)
+                    for i in range(iters):
+                        run(i)
+                    b.record(st)
+                    torch.cuda.synchronize()
+                    ms = a.elapsed_time(b) / iters
+                    best = ms if best is None else min(best, ms)
+                print(json.dumps({"sweep": f"{fname}->{oname}", "packed_bytes": nb, "rows": rows, "row_len": K,
+                                  "us_per_launch": best * 1e3, "output_gbps": numel * 2 / best / 1e6,
+                                  "hbm_gbps": per / best / 1e6, "frac_of_measured_peak": per / best / 1e6 / peak,
+                                  "l2_resident": resident, "buffers": nbuf}), flush=True)
+                del srcs, dsts
+        torch.cuda.empty_cache()
+    _native.check(L.pfhe_device_status(-1))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -632,8 +700,12 @@ def main() -> None:
                     help="skip the whole-model load legs (7B-shaped streaming, 70B-shaped sharded patch)")
     ap.add_argument("--kernel-case", default=None,
                     help="FORMAT:OUT:NUMEL[:LAUNCHES] -- run only a few launches of one kernel (for profilers)")
+    ap.add_argument("--sweep", action="store_true", help="kernel-roofline sweep over sizes, formats and dtypes")
+    ap.add_argument("--sweep-max-bytes", type=int, default=2 << 30)
     args = ap.parse_args()
-    if args.kernel_case:
+    if args.sweep:
+        run_sweep(args)
+    elif args.kernel_case:
         run_kernel_case(args.kernel_case)
     elif args.impl == "reference":
         run_reference_arm(args)

@@ -24,6 +24,7 @@ import logging
 import mmap
 import os
 import struct
+import threading
 from contextlib import contextmanager
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -91,6 +92,23 @@ _SCALARS = {
     GGUF_METADATA_VALUE_TYPE_UINT64: ("<Q", "<u8"), GGUF_METADATA_VALUE_TYPE_INT64: ("<q", "<i8"),
     GGUF_METADATA_VALUE_TYPE_FLOAT32: ("<f", "<f4"), GGUF_METADATA_VALUE_TYPE_FLOAT64: ("<d", "<f8"),
 }
+
+_DEFERRED_UNMAP_BYTES = 1 << 30
+_unmap_threads: List[threading.Thread] = []
+
+
+def wait_for_deferred_unmaps() -> None:
+    """Joins the background threads that unmap large files after their reader was closed."""
+    while _unmap_threads:
+        _unmap_threads.pop().join()
+
+
+def _close_map(m) -> None:
+    try:
+        m.close()
+    except BufferError:        # a caller still holds a view; the map dies with it
+        pass
+
 
 _TORCH_TO_OUT = {torch.float32: _native.OUT_F32, torch.float16: _native.OUT_F16, torch.bfloat16: _native.OUT_BF16}
 
@@ -254,13 +272,18 @@ class GGUFReader:
         return self
 
     def __exit__(self, *exc):
+        staged_from_map = self._view is not None
         self._view = None
         if self._mmap is not None:
-            try:
-                self._mmap.close()
-            except BufferError:        # a caller still holds a view; the map dies with it
-                pass
-            self._mmap = None
+            m, self._mmap = self._mmap, None
+            if staged_from_map and len(m) > _DEFERRED_UNMAP_BYTES:
+                # Unmapping a multi-gigabyte mapping whose pages were all touched takes
+                # hundreds of milliseconds of page-table teardown; nothing needs to wait for it.
+                t = threading.Thread(target=_close_map, args=(m,), daemon=True)
+                t.start()
+                _unmap_threads[:] = [x for x in _unmap_threads if x.is_alive()] + [t]
+            else:
+                _close_map(m)
         if self._file is not None:
             self._file.close()
             self._file = None

@@ -1,0 +1,80 @@
+"""Two-GPU checks (skipped on a single-GPU machine): row-sharded patch_context and the
+replicated layout completed by an NCCL all-gather.  Child processes, one per GPU; a rank only
+leaves between steps; NVLS is switched off so that an early exit cannot disturb the peers."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, path, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      LOCAL_WORLD_SIZE=str(world))
+    import datetime
+    import torch.distributed as dist
+    import pfhe_b200
+    from pfhe_b200 import gguf_loader as gl
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    ok = True
+    try:
+        with gl.GGUFReader(path) as r:
+            whole = {n: r.read_tensor(n, device=dev, dtype=torch.bfloat16) for n in r.tensors}
+        def module(shapes):
+            m = torch.nn.Module()
+            for n, shp in shapes.items():
+                sub = torch.nn.Module()
+                sub.register_parameter("weight", torch.nn.Parameter(torch.zeros(shp, dtype=torch.bfloat16, device=dev), requires_grad=False))
+                m.add_module(n.split(".")[0], sub)
+            return m
+        # sharded layout: no collective
+        shapes = {n: ((t.shape[0] // world,) + tuple(t.shape[1:]) if t.dim() >= 2 else tuple(t.shape)) for n, t in whole.items()}
+        m = module(shapes)
+        with pfhe_b200.GGUFModelPatcher(path).patch_context(m, device=str(dev), dtype=torch.bfloat16, shard=(rank, world)) as stats:
+            ok &= stats["loaded"] == len(whole)
+        for n, p in m.named_parameters():
+            t = whole[n]
+            want = t[rank * (t.shape[0] // world):(rank + 1) * (t.shape[0] // world)] if t.dim() >= 2 else t
+            ok &= bool(torch.equal(p.data.view(torch.int16), want.view(torch.int16)))
+        # replicated layout: decode own rows, all-gather the rest
+        m2 = module({n: tuple(t.shape) for n, t in whole.items()})
+        with pfhe_b200.GGUFModelPatcher(path).patch_context(m2, device=str(dev), dtype=torch.bfloat16, shard=(rank, world),
+                                                           replicate_group=dist.group.WORLD) as stats:
+            ok &= stats["loaded"] == len(whole)
+        torch.cuda.synchronize()
+        for n, p in m2.named_parameters():
+            ok &= bool(torch.equal(p.data.view(torch.int16), whole[n].view(torch.int16)))
+        dist.barrier()
+    finally:
+        q.put((rank, bool(ok)))
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_and_replicated_patch_two_gpus(tmp_path):
+    from pfhe_b200 import gguf_loader as gl, synth
+    path = str(tmp_path / "two.gguf")
+    specs = [synth.TensorSpec("a.weight", (512, 1024), gl.GGML_TYPE_Q4_1), synth.TensorSpec("b.weight", (300, 256), gl.GGML_TYPE_Q8_0),
+             synth.TensorSpec("c.weight", (64, 4096), gl.GGML_TYPE_Q4_0), synth.TensorSpec("n.weight", (1024,), gl.GGML_TYPE_F32)]
+    synth.write_gguf(path, specs, seed=12)
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, path, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert results == [(0, True), (1, True)]
