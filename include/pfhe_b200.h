@@ -32,6 +32,16 @@ enum pfhe_ggml_type {
     PFHE_TYPE_BF16 = 30
 };
 
+/*
+ * OR this into a ggml type to decode Q4_0 / Q4_1 in ggml's own element order
+ * (low nibbles of the block's 16 bytes are elements 0..15, high nibbles elements
+ * 16..31), which is what files written by llama.cpp contain.  Without the flag
+ * the reference's order is used: byte j gives elements 2j and 2j+1
+ * (gguf_loader.py:470-473, :514-516).  Ignored by the other types' kernels; only
+ * valid on PFHE_TYPE_Q4_0 and PFHE_TYPE_Q4_1.
+ */
+#define PFHE_TYPE_FLAG_GGML_ORDER 0x100
+
 /* Output element types: the torch dtypes read_tensor(dtype=...) accepts on this path. */
 enum pfhe_out_dtype { PFHE_OUT_F32 = 0, PFHE_OUT_F16 = 1, PFHE_OUT_BF16 = 2 };
 

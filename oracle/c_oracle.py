@@ -10,6 +10,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 _OUT = {"f32": 0, "f16": 1, "bf16": 2}
+GGML_ORDER = 0x100
 _NP_OUT = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16}
 _lib = None
 

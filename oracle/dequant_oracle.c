@@ -30,11 +30,17 @@ enum {
     ORACLE_BF16 = 30
 };
 
+/* OR-ed into Q4_0 / Q4_1: ggml's own element order (ggml-quants.c dequantize_row_q4_0 /
+ * dequantize_row_q4_1 as published: y[j] from the low nibble of qs[j], y[j+16] from the high
+ * nibble) instead of the reference's interleaved order.  Not a reference behaviour; pinned
+ * against the gguf-py package's dequantize() in tests/golden. */
+#define ORACLE_GGML_ORDER 0x100
+
 enum { ORACLE_OUT_F32 = 0, ORACLE_OUT_F16 = 1, ORACLE_OUT_BF16 = 2 };
 
 static int block_elems(int t)
 {
-    switch (t) {
+    switch (t & ~ORACLE_GGML_ORDER) {
     case ORACLE_F32: case ORACLE_F16: case ORACLE_BF16: return 1;
     case ORACLE_Q4_0: case ORACLE_Q4_1: case ORACLE_Q8_0: return 32;
     default: return 0;
@@ -43,7 +49,7 @@ static int block_elems(int t)
 
 static int block_bytes(int t)
 {
-    switch (t) {
+    switch (t & ~ORACLE_GGML_ORDER) {
     case ORACLE_F32: return 4;
     case ORACLE_F16: case ORACLE_BF16: return 2;
     case ORACLE_Q4_0: return 18;
@@ -122,6 +128,19 @@ static inline uint16_t rd_u16(const uint8_t *p) { return (uint16_t)(p[0] | ((uin
 /* One block of 32 values into v[32]; formulas follow the reference exactly. */
 static void decode_block(int t, const uint8_t *b, float *v)
 {
+    if (t & ORACLE_GGML_ORDER) {
+        /* same arithmetic as below, ggml's element order */
+        int q41 = (t & ~ORACLE_GGML_ORDER) == ORACLE_Q4_1;
+        double d = (double)half_to_f32(rd_u16(b));
+        double m = q41 ? (double)half_to_f32(rd_u16(b + 2)) : 0.0;
+        const uint8_t *qs = b + (q41 ? 4 : 2);
+        for (int j = 0; j < 16; j++) {
+            int lo = qs[j] & 0x0f, hi = qs[j] >> 4;
+            if (q41) { v[j] = (float)((double)lo * d + m); v[j + 16] = (float)((double)hi * d + m); }
+            else { v[j] = (float)((double)(lo - 8) * d); v[j + 16] = (float)((double)(hi - 8) * d); }
+        }
+        return;
+    }
     if (t == ORACLE_Q4_0) {
         /* gguf_loader.py:451-474: out[2j] = ((qs[j]&15)-8)*d, out[2j+1] = ((qs[j]>>4)-8)*d.
          * The reference multiplies int16 by a Python float (float64) and stores to
@@ -161,6 +180,8 @@ int oracle_decode_f32(int ggml_type, const uint8_t *src, int64_t src_bytes,
 {
     int64_t need = oracle_nbytes(ggml_type, numel);
     if (need < 0) return -1;
+    if ((ggml_type & ORACLE_GGML_ORDER) && (ggml_type & ~ORACLE_GGML_ORDER) != ORACLE_Q4_0 &&
+        (ggml_type & ~ORACLE_GGML_ORDER) != ORACLE_Q4_1) return -1;
     if (src_bytes < need) return -2;
     (void)n_threads;
 #ifdef _OPENMP

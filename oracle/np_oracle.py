@@ -10,12 +10,16 @@ import numpy as np
 # ggml type ids and (elements per block, bytes per block):
 # src/phfe/inference/gguf_loader.py:33-65
 F32, F16, Q4_0, Q4_1, Q8_0, BF16 = 0, 1, 2, 3, 8, 30
+# OR-ed into Q4_0 / Q4_1: ggml's own element order (low nibbles -> elements 0..15, high nibbles ->
+# 16..31, as in ggml's published dequantize_row_q4_0/q4_1) instead of the reference's interleaving.
+GGML_ORDER = 0x100
 BLOCK_GEOMETRY = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q4_0: (32, 18), Q4_1: (32, 20), Q8_0: (32, 34)}
 TYPE_NAMES = {F32: "F32", F16: "F16", BF16: "BF16", Q4_0: "Q4_0", Q4_1: "Q4_1", Q8_0: "Q8_0"}
 
 
 def nbytes(ggml_type: int, numel: int) -> int:
     """``GGUFTensorInfo.nbytes`` (gguf_loader.py:131-139)."""
+    ggml_type &= ~GGML_ORDER
     if ggml_type not in BLOCK_GEOMETRY:
         raise ValueError(f"Unknown dtype {ggml_type} for size calculation")
     be, bb = BLOCK_GEOMETRY[ggml_type]
@@ -42,6 +46,14 @@ def _scale_f64(blocks: np.ndarray, col: int) -> np.ndarray:
 
 def decode_f32(ggml_type: int, data, numel: int) -> np.ndarray:
     """The six decode functions of gguf_loader.py:407-554; returns float32[numel]."""
+    if ggml_type & GGML_ORDER:
+        base = ggml_type & ~GGML_ORDER
+        if base not in (Q4_0, Q4_1):
+            raise NotImplementedError(f"ggml element order applies to Q4_0/Q4_1, not type {base}")
+        n_blocks = -(-numel // 32)
+        v = decode_f32(base, data, n_blocks * 32).reshape(n_blocks, 16, 2)
+        # interleaved slot 2j holds the low nibble of byte j, slot 2j+1 the high nibble
+        return np.concatenate([v[:, :, 0], v[:, :, 1]], axis=1).reshape(-1)[:numel].copy()
     if ggml_type == F32:      # :407-410
         return _as_u8(data)[: numel * 4].view("<f4").copy()
     if ggml_type == F16:      # :413-416  exact widening

@@ -20,6 +20,7 @@ ERR_BAD_ARG, ERR_CUDA, ERR_TIMEOUT, ERR_DEVICE_WAIT = -5, -6, -7, -8
 OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
 
 NOALLOC_MAX_PACKED_BYTES = 8 * 1024 * 1024   # PFHE_NOALLOC_MAX_PACKED_BYTES
+TYPE_FLAG_GGML_ORDER = 0x100                 # PFHE_TYPE_FLAG_GGML_ORDER
 
 # Every symbol include/pfhe_b200.h declares.
 EXPORTED_SYMBOLS = (

@@ -146,8 +146,8 @@ int type_geometry(int t, int *elems, int *bytes)
     switch (t) {
     case T_F32: *elems = 1; *bytes = 4; return PFHE_OK;
     case T_F16: case T_BF16: *elems = 1; *bytes = 2; return PFHE_OK;
-    case T_Q4_0: *elems = 32; *bytes = 18; return PFHE_OK;
-    case T_Q4_1: *elems = 32; *bytes = 20; return PFHE_OK;
+    case T_Q4_0: case T_Q4_0G: *elems = 32; *bytes = 18; return PFHE_OK;
+    case T_Q4_1: case T_Q4_1G: *elems = 32; *bytes = 20; return PFHE_OK;
     case T_Q8_0: *elems = 32; *bytes = 34; return PFHE_OK;
     default:
         set_error("ggml type %d is not one of F32, F16, BF16, Q4_0, Q4_1, Q8_0", t);
@@ -287,6 +287,8 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     bool ok = false;
     if (ggml_type == T_Q4_0) ok = pick_block<T_Q4_0>(mid, out, &k);
     else if (ggml_type == T_Q4_1) ok = pick_block<T_Q4_1>(mid, out, &k);
+    else if (ggml_type == T_Q4_0G) ok = pick_block<T_Q4_0G>(mid, out, &k);
+    else if (ggml_type == T_Q4_1G) ok = pick_block<T_Q4_1G>(mid, out, &k);
     else ok = pick_block<T_Q8_0>(mid, out, &k);
     if (!ok) { set_error("no kernel"); return PFHE_ERR_BAD_DTYPE; }
 

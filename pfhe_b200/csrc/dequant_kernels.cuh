@@ -23,6 +23,10 @@
 namespace pfhe {
 
 enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q8_0 = 8, T_BF16 = 30 };
+// Q4_0 / Q4_1 with ggml's own element order (low nibbles of bytes 0..15 are elements
+// 0..15, high nibbles elements 16..31) instead of the reference's interleaved order.
+// Selected with PFHE_TYPE_FLAG_GGML_ORDER on the ggml type.
+enum : int { T_ORDER_FLAG = 0x100, T_Q4_0G = T_Q4_0 | T_ORDER_FLAG, T_Q4_1G = T_Q4_1 | T_ORDER_FLAG };
 enum : int { O_F32 = 0, O_F16 = 1, O_BF16 = 2 };
 
 // Device-side status codes written to the status word.
@@ -35,6 +39,8 @@ template <> struct Fmt<T_BF16> { static constexpr int kElems = 1,  kBytes = 2;  
 template <> struct Fmt<T_Q4_0> { static constexpr int kElems = 32, kBytes = 18; };
 template <> struct Fmt<T_Q4_1> { static constexpr int kElems = 32, kBytes = 20; };
 template <> struct Fmt<T_Q8_0> { static constexpr int kElems = 32, kBytes = 34; };
+template <> struct Fmt<T_Q4_0G> { static constexpr int kElems = 32, kBytes = 18; };
+template <> struct Fmt<T_Q4_1G> { static constexpr int kElems = 32, kBytes = 20; };
 
 template <int O> struct OutT;
 template <> struct OutT<O_F32>  { using type = float;    static constexpr int kSize = 4; };
@@ -140,7 +146,63 @@ template <int T, int MID, int OUT, bool kShared>
 __device__ __forceinline__ uint4 decode_unit(const uint8_t *blk, int c)
 {
     uint4 r;
-    if constexpr (T == T_Q4_0 || T == T_Q4_1) {
+    if constexpr (T == T_Q4_0G || T == T_Q4_1G) {
+        // ggml order: a unit takes either the low or the high nibbles of a run of bytes.
+        constexpr bool kHasMin = (T == T_Q4_1G);
+        constexpr int kQs = kHasMin ? 4 : 2;
+        constexpr float kBias = kHasMin ? 0.0f : 8.0f;
+        const uint32_t dbits = ld16<kShared>(blk);
+        if constexpr (OUT == O_F32) {
+            // unit c of 8: elements 4c..4c+3 = low (c < 4) or high nibbles of bytes 4(c&3)..4(c&3)+3
+            const uint8_t *q = blk + kQs + 4 * (c & 3);
+            const uint32_t raw = ld16<kShared>(q) | (ld16<kShared>(q + 2) << 16);
+            const uint32_t w = (raw >> ((c >> 2) * 4)) & 0x0F0F0F0Fu;      // one nibble per byte
+            const float d = half_bits_to_f32(dbits);
+            float v0 = __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)), 8388608.0f + kBias);
+            float v1 = __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)), 8388608.0f + kBias);
+            float v2 = __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)), 8388608.0f + kBias);
+            float v3 = __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)), 8388608.0f + kBias);
+            if constexpr (kHasMin) {
+                const float m = half_bits_to_f32(ld16<kShared>(blk + 2));
+                v0 = __fmaf_rn(v0, d, m); v1 = __fmaf_rn(v1, d, m); v2 = __fmaf_rn(v2, d, m); v3 = __fmaf_rn(v3, d, m);
+            } else {
+                v0 = __fmul_rn(v0, d); v1 = __fmul_rn(v1, d); v2 = __fmul_rn(v2, d); v3 = __fmul_rn(v3, d);
+            }
+            r.x = __float_as_uint(round_via<MID>(v0)); r.y = __float_as_uint(round_via<MID>(v1));
+            r.z = __float_as_uint(round_via<MID>(v2)); r.w = __float_as_uint(round_via<MID>(v3));
+        } else {
+            // unit c of 4: elements 8c..8c+7 = low (c < 2) or high nibbles of bytes 8(c&1)..8(c&1)+7
+            const uint8_t *q = blk + kQs + 8 * (c & 1);
+            const uint32_t sh = (c >> 1) * 4;
+            const uint32_t w0 = ((ld16<kShared>(q) | (ld16<kShared>(q + 2) << 16)) >> sh) & 0x0F0F0F0Fu;
+            const uint32_t w1 = ((ld16<kShared>(q + 4) | (ld16<kShared>(q + 6) << 16)) >> sh) & 0x0F0F0F0Fu;
+            if constexpr (!kHasMin && MID == O_F16 && OUT == O_F16) {
+                const uint32_t d2 = dbits * 0x10001u;
+                const uint32_t bias = 0x64086408u;                         // half2(1032, 1032)
+                r.x = h2_sub_mul(__byte_perm(w0, 0x64646464u, 0x4140), bias, d2);
+                r.y = h2_sub_mul(__byte_perm(w0, 0x64646464u, 0x4342), bias, d2);
+                r.z = h2_sub_mul(__byte_perm(w1, 0x64646464u, 0x4140), bias, d2);
+                r.w = h2_sub_mul(__byte_perm(w1, 0x64646464u, 0x4342), bias, d2);
+            } else {
+                const float d = half_bits_to_f32(dbits);
+                float v[8];
+                v[0] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7540)); v[1] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7541));
+                v[2] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7542)); v[3] = __uint_as_float(__byte_perm(w0, 0x4B000000u, 0x7543));
+                v[4] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7540)); v[5] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7541));
+                v[6] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7542)); v[7] = __uint_as_float(__byte_perm(w1, 0x4B000000u, 0x7543));
+                if constexpr (kHasMin) {
+                    const float m = half_bits_to_f32(ld16<kShared>(blk + 2));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = __fmaf_rn(__fsub_rn(v[i], 8388608.0f), d, m);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fsub_rn(v[i], 8388616.0f), d);
+                }
+                r.x = pack2<MID, OUT>(v[0], v[1]); r.y = pack2<MID, OUT>(v[2], v[3]);
+                r.z = pack2<MID, OUT>(v[4], v[5]); r.w = pack2<MID, OUT>(v[6], v[7]);
+            }
+        }
+    } else if constexpr (T == T_Q4_0 || T == T_Q4_1) {
         constexpr int kQs = (T == T_Q4_0) ? 2 : 4;
         const uint32_t dbits = ld16<kShared>(blk);
         if constexpr (OUT == O_F32) {
@@ -251,6 +313,13 @@ template <int T> __device__ __forceinline__ float decode_element_bytes(const uin
         const float d = half_bits_to_f32((uint32_t)b[0] | ((uint32_t)b[1] << 8));
         if constexpr (T == T_Q8_0) {
             return __fmul_rn((float)(int)(int8_t)b[2 + k], d);
+        } else if constexpr (T == T_Q4_0G) {
+            const uint32_t byte = b[2 + (k & 15)];
+            return __fmul_rn((float)((int)((k & 16) ? (byte >> 4) : (byte & 15)) - 8), d);
+        } else if constexpr (T == T_Q4_1G) {
+            const float m = half_bits_to_f32((uint32_t)b[2] | ((uint32_t)b[3] << 8));
+            const uint32_t byte = b[4 + (k & 15)];
+            return __fmaf_rn((float)(int)((k & 16) ? (byte >> 4) : (byte & 15)), d, m);
         } else if constexpr (T == T_Q4_0) {
             const uint32_t byte = b[2 + (k >> 1)];
             const int q = (int)((k & 1) ? (byte >> 4) : (byte & 15)) - 8;
@@ -525,7 +594,7 @@ struct BatchKernelArgs {
 
 __device__ __forceinline__ int kind_block_bytes(int kind)
 {
-    const int t = kind >> 2;
+    const int t = (kind >> 2) & ~T_ORDER_FLAG;
     return t == T_Q4_0 ? 18 : (t == T_Q4_1 ? 20 : 34);
 }
 
@@ -581,6 +650,8 @@ __global__ void __launch_bounds__(512) dequant_blocks_batch(const __grid_constan
             PFHE_TILE(T_Q4_0, O_F32) PFHE_TILE(T_Q4_0, O_F16) PFHE_TILE(T_Q4_0, O_BF16)
             PFHE_TILE(T_Q4_1, O_F32) PFHE_TILE(T_Q4_1, O_F16) PFHE_TILE(T_Q4_1, O_BF16)
             PFHE_TILE(T_Q8_0, O_F32) PFHE_TILE(T_Q8_0, O_F16) PFHE_TILE(T_Q8_0, O_BF16)
+            PFHE_TILE(T_Q4_0G, O_F32) PFHE_TILE(T_Q4_0G, O_F16) PFHE_TILE(T_Q4_0G, O_BF16)
+            PFHE_TILE(T_Q4_1G, O_F32) PFHE_TILE(T_Q4_1G, O_F16) PFHE_TILE(T_Q4_1G, O_BF16)
 #undef PFHE_TILE
             default: break;
         }

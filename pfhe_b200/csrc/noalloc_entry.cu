@@ -153,6 +153,8 @@ extern "C" int pfhe_dequant_from_host_noalloc(int ggml_type, int out_dtype, cons
     switch (ggml_type) {
     case T_Q4_0: dispatch_out<T_Q4_0>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
     case T_Q4_1: dispatch_out<T_Q4_1>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q4_0G: dispatch_out<T_Q4_0G>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q4_1G: dispatch_out<T_Q4_1G>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
     case T_Q8_0: dispatch_out<T_Q8_0>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
     case T_F16: dispatch_out<T_F16>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
     case T_BF16: dispatch_out<T_BF16>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;

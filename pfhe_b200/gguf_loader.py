@@ -253,8 +253,14 @@ class GGUFReader:
             w = reader.read_tensor("blk.0.attn_q.weight", device="cuda", dtype=torch.float16)
     """
 
-    def __init__(self, path: str | Path):
+    def __init__(self, path: str | Path, *, nibble_order: str = "reference"):
+        """nibble_order: "reference" decodes Q4_0/Q4_1 as the reference does (byte j of a block
+        gives elements 2j and 2j+1); "ggml" uses ggml's own order (low nibbles are elements
+        0..15, high nibbles 16..31), which is what files written by llama.cpp contain."""
+        if nibble_order not in ("reference", "ggml"):
+            raise ValueError(f"nibble_order must be 'reference' or 'ggml', not {nibble_order!r}")
         self.path = Path(path)
+        self.nibble_order = nibble_order
         self._file = None
         self._mmap = None
         self._view: Optional[np.ndarray] = None      # uint8 view of the mmap (for host addresses)
@@ -450,7 +456,10 @@ class GGUFReader:
                 raise ValueError(f"Data too short: {max(len(self._mmap) - start, 0)} < {nbytes}")
             with torch.cuda.device(cuda_dev):
                 stager = _Stager.get(cuda_dev.index)
-                args = (nbytes, info.dtype, _TORCH_TO_OUT[dtype], _TORCH_TO_OUT[target.dtype], target, numel)
+                kernel_type = info.dtype
+                if self.nibble_order == "ggml" and info.dtype in (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1):
+                    kernel_type |= _native.TYPE_FLAG_GGML_ORDER
+                args = (nbytes, kernel_type, _TORCH_TO_OUT[dtype], _TORCH_TO_OUT[target.dtype], target, numel)
                 if _Stager.source == "pread":
                     stager.submit_fd(self._file.fileno(), start, *args)
                 else:   # host threads copy out of the mapping (first-touch faults happen in those threads)
@@ -473,9 +482,9 @@ class GGUFReader:
 # ---------------------------------------------------------------------------
 @contextmanager
 def tensor_loading_context(path: str | Path, device: str = "cpu",
-                           dtype: torch.dtype = torch.float32) -> Iterator[GGUFReader]:
+                           dtype: torch.dtype = torch.float32, *, nibble_order: str = "reference") -> Iterator[GGUFReader]:
     """Yields an opened reader.  ``device``/``dtype`` are accepted and unused, as in the reference (:561-575)."""
-    with GGUFReader(path) as reader:
+    with GGUFReader(path, nibble_order=nibble_order) as reader:
         yield reader
 
 
@@ -483,15 +492,16 @@ class StreamingDequantizer:
     """Streams decoded tensors to the GPU in batches (reference :603-660)."""
 
     def __init__(self, path: str | Path, batch_size: int = 4, device: str = "cuda",
-                 dtype: torch.dtype = torch.float16):
+                 dtype: torch.dtype = torch.float16, *, nibble_order: str = "reference"):
         self.path = Path(path)
         self.batch_size = batch_size
         self.device = device
         self.dtype = dtype
+        self.nibble_order = nibble_order
         self._reader: Optional[GGUFReader] = None
 
     def open(self):
-        self._reader = GGUFReader(self.path)
+        self._reader = GGUFReader(self.path, nibble_order=self.nibble_order)
         self._reader.__enter__()
 
     def close(self):
@@ -524,8 +534,9 @@ class StreamingDequantizer:
 
 @contextmanager
 def streaming_dequant_context(path: str | Path, batch_size: int = 4, device: str = "cuda",
-                              dtype: torch.dtype = torch.float16) -> Iterator[StreamingDequantizer]:
-    streamer = StreamingDequantizer(path, batch_size, device, dtype)
+                              dtype: torch.dtype = torch.float16, *,
+                              nibble_order: str = "reference") -> Iterator[StreamingDequantizer]:
+    streamer = StreamingDequantizer(path, batch_size, device, dtype, nibble_order=nibble_order)
     streamer.open()
     try:
         yield streamer
@@ -539,9 +550,11 @@ def streaming_dequant_context(path: str | Path, batch_size: int = 4, device: str
 class GGUFModelPatcher:
     """Writes GGUF tensors into the parameters of a torch module."""
 
-    def __init__(self, gguf_path: str | Path, name_mapping: Optional[Dict[str, str]] = None):
+    def __init__(self, gguf_path: str | Path, name_mapping: Optional[Dict[str, str]] = None, *,
+                 nibble_order: str = "reference"):
         self.gguf_path = Path(gguf_path)
         self.name_mapping = name_mapping or {}
+        self.nibble_order = nibble_order
         self._reader: Optional[GGUFReader] = None
 
     def _map_name(self, gguf_name: str) -> str:
@@ -575,7 +588,7 @@ class GGUFModelPatcher:
         stats: Dict[str, Any] = {"loaded": 0, "skipped": 0, "missing": [], "unexpected": []}
         params = dict(model.named_parameters())
         gathers = []
-        with GGUFReader(self.gguf_path) as reader:
+        with GGUFReader(self.gguf_path, nibble_order=self.nibble_order) as reader:
             self._reader = reader
             for gguf_name, info in reader.tensors.items():
                 torch_name = self._map_name(gguf_name)

@@ -1,0 +1,79 @@
+"""Loading a Llama/Gemma-style torch module from a GGUF file -- the caller side of the decode path.
+
+The reference's ``GGUFModel.from_gguf`` (src/phfe/inference/model.py:313-371) builds the module on
+the CPU in fp32, reads every tensor with ``reader.read_tensor(name, device, dtype)``, copies it into
+the CPU parameter and finally moves the whole module to the device.  Here the module goes to the
+device first and every tensor is decoded straight into its parameter's storage; the parameter
+values are the same bits (one rounding to ``dtype``).  The model classes themselves are not part of
+this package: any module whose parameter names follow the reference's layout works.
+"""
+from __future__ import annotations
+
+import logging
+import re
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .gguf_loader import GGUFModelPatcher, GGUFReader
+
+logger = logging.getLogger(__name__)
+
+_TOP_LEVEL = {
+    "token_embd.weight": "embed_tokens.weight",
+    "output.weight": "lm_head.weight",
+    "output_norm.weight": "norm.weight",
+}
+
+# blk.{i}.<component> -> layers.{i}.<suffix>   (reference model.py:377-420)
+_PER_LAYER = {
+    "attn_q.weight": "self_attn.q_proj.weight",
+    "attn_k.weight": "self_attn.k_proj.weight",
+    "attn_v.weight": "self_attn.v_proj.weight",
+    "attn_output.weight": "self_attn.o_proj.weight",
+    "ffn_gate.weight": "mlp.gate_proj.weight",
+    "ffn_up.weight": "mlp.up_proj.weight",
+    "ffn_down.weight": "mlp.down_proj.weight",
+    "attn_norm.weight": "input_layernorm.weight",
+    "ffn_norm.weight": "post_attention_layernorm.weight",
+    "attn_q_norm.weight": "self_attn.q_norm.weight",
+    "attn_k_norm.weight": "self_attn.k_norm.weight",
+    "post_attention_norm.weight": "post_attention_norm.weight",
+    "post_ffw_norm.weight": "post_ffn_norm.weight",
+}
+_BLOCK = re.compile(r"blk\.(\d+)\.(.+)")
+
+
+def map_tensor_name(gguf_name: str) -> Optional[str]:
+    """GGUF tensor name -> module parameter name, or None for tensors the model does not hold."""
+    if gguf_name in _TOP_LEVEL:
+        return _TOP_LEVEL[gguf_name]
+    m = _BLOCK.match(gguf_name)
+    if m:
+        suffix = _PER_LAYER.get(m.group(2))
+        return None if suffix is None else f"layers.{m.group(1)}.{suffix}"
+    return None
+
+
+def load_model_weights(model: torch.nn.Module, path, device: str = "cuda", dtype: torch.dtype = torch.float16,
+                       shard: Optional[Tuple[int, int]] = None, nibble_order: str = "reference") -> Dict[str, int]:
+    """Fills ``model`` from the GGUF file at ``path`` and returns ``{"loaded", "skipped"}``.
+
+    The module is moved to ``device``/``dtype`` first (what the reference does last), then every
+    mapped tensor whose shape matches is decoded in place.  Unmapped names, names the module does
+    not have and shape mismatches count as skipped, as in the reference loop.
+    ``shard=(rank, world_size)`` loads row shards into parameters that hold ``rows // world_size`` rows.
+    """
+    model.to(device=device, dtype=dtype)
+    with GGUFReader(path) as reader:
+        mapping = {name: map_tensor_name(name) for name in reader.tensors}
+    usable = {g: p for g, p in mapping.items() if p is not None}
+    unmapped = len(mapping) - len(usable)
+    # names with no mapping must not fall through to the patcher's own default rule
+    patcher = GGUFModelPatcher(path, {**{g: f"\0unmapped.{g}" for g in mapping if g not in usable}, **usable},
+                               nibble_order=nibble_order)
+    with patcher.patch_context(model, device=device, dtype=dtype, shard=shard) as stats:
+        pass
+    logger.info(f"Loaded {stats['loaded']} tensors, skipped {stats['skipped']}")
+    assert stats["skipped"] >= unmapped
+    return {"loaded": stats["loaded"], "skipped": stats["skipped"]}

@@ -16,6 +16,9 @@ Files written:
   mini.gguf          7-tensor file covering all six types and every metadata kind
   mini_expected.json what the reference's GGUFReader parsed from mini.gguf
   mini_tensors.npz   reference read_tensor(...) of every tensor in mini.gguf
+  decode_Q4_x_ggml_order.npz  the same packed inputs decoded in ggml's own nibble order by the gguf-py
+                     package (an independent implementation; the reference has no such mode)
+  name_map.json      GGUFModel._map_tensor_name(...) of the reference for a list of tensor names
 """
 from __future__ import annotations
 
@@ -114,6 +117,22 @@ def main(ref_root: str) -> None:
         np.savez_compressed(os.path.join(HERE, f"decode_{NAMES[fmt]}.npz"), **out)
         print(NAMES[fmt], numel, "elements")
 
+    # --- ggml's own nibble order (not a reference behaviour): pinned to the gguf-py package -------
+    try:
+        import gguf
+        from gguf import quants
+        for fmt, gtype in ((Q4_0, gguf.GGMLQuantizationType.Q4_0), (Q4_1, gguf.GGMLQuantizationType.Q4_1)):
+            g = np.load(os.path.join(HERE, f"decode_{NAMES[fmt]}.npz"))
+            raw = g["raw"]
+            n_blocks = raw.size // {Q4_0: 18, Q4_1: 20}[fmt]
+            v = torch.from_numpy(quants.dequantize(raw, gtype).reshape(-1).astype(np.float32)[: int(g["numel"])].copy())
+            np.savez_compressed(os.path.join(HERE, f"decode_{NAMES[fmt]}_ggml_order.npz"), raw=raw, numel=g["numel"],
+                                f32=bits(v), f16=bits(v.to(torch.float16)), bf16=bits(v.to(torch.bfloat16)),
+                                source=np.array(f"gguf-py {getattr(gguf, '__version__', '0.19.0')} quants.dequantize"))
+            print(NAMES[fmt], "ggml order", n_blocks, "blocks")
+    except ImportError:
+        print("gguf-py not installed: ggml-order fixtures not regenerated")
+
     # --- a small file through the reference's parser and read_tensor ---------
     from pfhe_b200 import synth
     specs = [
@@ -155,6 +174,16 @@ def main(ref_root: str) -> None:
             for k, dt in TORCH.items():
                 tens[f"{n}|{k}"] = bits(r.read_tensor(n, device="cpu", dtype=dt).reshape(-1))
             tens[f"{n}|raw"] = np.frombuffer(r.read_tensor_raw(n), dtype=np.uint8)
+    # --- the caller's name map (model.py:377-420) ---------------------------------------------------
+    from phfe.inference.model import GGUFModel
+    probe = ["token_embd.weight", "output.weight", "output_norm.weight", "rope_freqs.weight", "blk.0.attn_q.weight",
+             "blk.12.attn_k.weight", "blk.3.attn_v.weight", "blk.79.attn_output.weight", "blk.1.ffn_gate.weight",
+             "blk.1.ffn_up.weight", "blk.1.ffn_down.weight", "blk.5.attn_norm.weight", "blk.5.ffn_norm.weight",
+             "blk.2.attn_q_norm.weight", "blk.2.attn_k_norm.weight", "blk.2.post_attention_norm.weight",
+             "blk.2.post_ffw_norm.weight", "blk.2.attn_rot_embd", "blk.x.attn_q.weight", "blk.7.ffn_gate_inp.weight",
+             "model.layers.0.w", "output.bias", "xblk.1.attn_q.weight"]
+    with open(os.path.join(HERE, "name_map.json"), "w") as f:
+        json.dump({n: GGUFModel._map_tensor_name(n) for n in probe}, f, indent=1)
     with open(os.path.join(HERE, "mini_expected.json"), "w") as f:
         json.dump(expected, f, indent=1, ensure_ascii=True)
     np.savez_compressed(os.path.join(HERE, "mini_tensors.npz"), **tens)

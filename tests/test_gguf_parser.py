@@ -164,3 +164,12 @@ def test_writer_roundtrip_large_metadata(tmp_path):
         last = list(r.tensors.values())[-1]
         assert r.header.tensor_data_offset + last.offset + last.nbytes == os.path.getsize(p)
         assert all(t.offset % 32 == 0 for t in r.tensors.values())
+
+
+def test_caller_name_map_matches_reference(golden_dir):
+    from pfhe_b200.model_loader import map_tensor_name
+    with open(os.path.join(golden_dir, "name_map.json")) as f:
+        expected = json.load(f)
+    assert len(expected) > 20
+    for gguf_name, want in expected.items():
+        assert map_tensor_name(gguf_name) == want, gguf_name

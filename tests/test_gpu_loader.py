@@ -241,3 +241,78 @@ def test_llama70b_shaped_layer_row_sharded_eight_ways(tmp_path_factory):
     finally:
         if os.path.exists(path):
             os.unlink(path)
+
+
+class _RefLayout(torch.nn.Module):
+    """A module with the parameter names of the reference's GGUFModel (no forward needed)."""
+    def __init__(self, shape, rows_div=1):
+        super().__init__()
+        H, F, V = shape.hidden, shape.ffn, shape.vocab
+        kv = shape.n_kv_heads * shape.head_dim
+        lin = lambda o, i: torch.nn.Linear(i, o // rows_div, bias=False)
+        self.embed_tokens = torch.nn.Embedding(V // rows_div, H)
+        self.layers = torch.nn.ModuleList()
+        for _ in range(shape.n_layers):
+            blk = torch.nn.Module()
+            blk.self_attn = torch.nn.Module()
+            blk.self_attn.q_proj, blk.self_attn.k_proj = lin(H, H), lin(kv, H)
+            blk.self_attn.v_proj, blk.self_attn.o_proj = lin(kv, H), lin(H, H)
+            blk.mlp = torch.nn.Module()
+            blk.mlp.gate_proj, blk.mlp.up_proj, blk.mlp.down_proj = lin(F, H), lin(F, H), lin(H, F)
+            blk.input_layernorm = torch.nn.LayerNorm(H, bias=False)
+            blk.post_attention_layernorm = torch.nn.LayerNorm(H, bias=False)
+            self.layers.append(blk)
+        self.norm = torch.nn.LayerNorm(H, bias=False)
+        self.lm_head = lin(V, H)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_load_model_weights_like_from_gguf(small_llama, dtype):
+    from pfhe_b200.model_loader import load_model_weights, map_tensor_name
+    path, shape = small_llama
+    model = _RefLayout(shape)                       # CPU, fp32, as the reference builds it
+    stats = load_model_weights(model, path, device="cuda", dtype=dtype)
+    assert stats == {"loaded": 2 * 9 + 3, "skipped": 0}
+    key = "f16" if dtype == torch.float16 else "bf16"
+    params = dict(model.named_parameters())
+    with gl.GGUFReader(path) as r:
+        for gname in r.tensors:
+            p = params[map_tensor_name(gname)]
+            assert p.is_cuda and p.dtype == dtype
+            assert_same_bits(to_bits(p.data), _oracle_tensor(r, gname, key), key, gname)
+    # row-sharded variant: every 2-D parameter holds rows // 2
+    half = _RefLayout(shape, rows_div=2)
+    stats = load_model_weights(half, path, device="cuda", dtype=dtype, shard=(1, 2))
+    assert stats["loaded"] == 2 * 9 + 3
+    with gl.GGUFReader(path) as r:
+        want = _oracle_tensor(r, "blk.1.ffn_down.weight", key).reshape(shape.hidden, shape.ffn)
+        got = dict(half.named_parameters())["layers.1.mlp.down_proj.weight"]
+        assert_same_bits(to_bits(got.data), want[shape.hidden // 2:].reshape(-1), key, "shard 1 of ffn_down")
+
+
+def test_nibble_order_option(small_llama):
+    """nibble_order="ggml" through every public entry; the default stays the reference's order."""
+    path, shape = small_llama
+    name = "blk.0.ffn_gate.weight"
+    with gl.GGUFReader(path) as r:
+        info = r.tensors[name]
+        raw = r.read_tensor_raw(name)
+    want_ggml = np_oracle.read_tensor(info.dtype | np_oracle.GGML_ORDER, raw, info.numel, "f16")
+    want_ref = np_oracle.read_tensor(info.dtype, raw, info.numel, "f16")
+    assert not np.array_equal(want_ggml.view(np.uint16), want_ref.view(np.uint16))
+    with pfhe_b200.tensor_loading_context(path, nibble_order="ggml") as r:
+        assert_same_bits(to_bits(r.read_tensor(name, device="cuda", dtype=torch.float16)), want_ggml, "f16")
+        # Q8_0 and F32 tensors are unaffected
+        assert_same_bits(to_bits(r.read_tensor("token_embd.weight", device="cuda", dtype=torch.float16)),
+                         _oracle_tensor(r, "token_embd.weight", "f16"), "f16")
+    with pfhe_b200.tensor_loading_context(path) as r:
+        assert_same_bits(to_bits(r.read_tensor(name, device="cuda", dtype=torch.float16)), want_ref, "f16")
+    with pfhe_b200.streaming_dequant_context(path, batch_size=32, dtype=torch.float16, nibble_order="ggml") as s:
+        batch = next(s.iter_batches())
+        assert_same_bits(to_bits(batch[name]), want_ggml, "f16")
+    lin = torch.nn.Linear(shape.hidden, shape.ffn, bias=False, device="cuda", dtype=torch.float16)
+    with pfhe_b200.GGUFModelPatcher(path, {name: "weight"}, nibble_order="ggml").patch_context(lin) as stats:
+        assert stats["loaded"] == 1
+    assert_same_bits(to_bits(lin.weight.data), want_ggml, "f16")
+    with pytest.raises(ValueError):
+        gl.GGUFReader(path, nibble_order="other")

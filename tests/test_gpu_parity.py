@@ -252,3 +252,49 @@ def test_tile_schedules(schedule, exact_tiles):
     torch.cuda.synchronize()
     _native.check(L.pfhe_device_status(-1))
     assert_same_bits(to_bits(dst), want, "bf16", f"schedule {schedule} exact {exact_tiles}")
+
+
+# --- opt-in ggml nibble order ---------------------------------------------------------------------
+@pytest.mark.parametrize("fmt", ["Q4_0", "Q4_1"])
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+@pytest.mark.parametrize("variant", ["default", "direct", "staged_out", "per_element", "staged_small_tiles"])
+def test_ggml_order_golden(fmt, dtype, variant):
+    import os
+    from conftest import GOLDEN
+    g = np.load(os.path.join(GOLDEN, f"decode_{fmt}_ggml_order.npz"))
+    got = decode_on_gpu(FORMATS[fmt] | _native.TYPE_FLAG_GGML_ORDER, g["raw"], int(g["numel"]), dtype, cfg=VARIANTS[variant])
+    assert_same_bits(to_bits(got), g[dtype], dtype, f"{fmt} ggml order ->{dtype} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", ["Q4_0", "Q4_1"])
+def test_ggml_order_large_and_skewed(fmt):
+    t = FORMATS[fmt] | _native.TYPE_FLAG_GGML_ORDER
+    numel = 4096 * 1000 + 17
+    raw = synth.random_packed(FORMATS[fmt], numel, np.random.default_rng(31))
+    for dtype in OUT_DTYPES:
+        want = c_oracle.read_tensor(t, raw, numel, dtype, n_threads=8)
+        for skew in (0, 6):
+            got = decode_on_gpu(t, raw, numel, dtype, skew=skew)
+            assert_same_bits(to_bits(got), want, dtype, f"{fmt} ggml order skew {skew}->{dtype}")
+    with pytest.raises(NotImplementedError):
+        decode_on_gpu(FORMATS["Q8_0"] | _native.TYPE_FLAG_GGML_ORDER, raw, 32, "f16")
+
+
+def test_ggml_order_in_a_batch():
+    from gpu_util import device_bytes
+    L = _native.lib()
+    cases = [("Q4_0", True), ("Q4_0", False), ("Q4_1", True), ("Q8_0", False), ("Q4_1", False)]
+    numel = 32 * 5000
+    descs = (_native.TensorDesc * len(cases))()
+    keep, wants = [], []
+    for i, (fmt, ggml) in enumerate(cases):
+        raw = synth.random_packed(FORMATS[fmt], numel, np.random.default_rng(40 + i))
+        t = FORMATS[fmt] | (_native.TYPE_FLAG_GGML_ORDER if ggml else 0)
+        src, dst = device_bytes(raw), torch.empty(numel, dtype=torch.bfloat16, device="cuda")
+        keep.append((src, dst))
+        wants.append(np_oracle.read_tensor(t, raw, numel, "bf16"))
+        descs[i] = _native.TensorDesc(t, _native.OUT_BF16, src.data_ptr(), src.numel(), dst.data_ptr(), numel * 2, numel)
+    _native.check(L.pfhe_dequant_launch_batch(descs, len(cases), None))
+    torch.cuda.synchronize()
+    for (src, dst), want, case in zip(keep, wants, cases):
+        assert_same_bits(to_bits(dst), want, "bf16", str(case))

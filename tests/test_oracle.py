@@ -87,3 +87,23 @@ def test_oracles_agree_on_seeded_blocks(fmt):
         a = np_oracle.read_tensor(t, raw, numel, dtype)
         b = c_oracle.read_tensor(t, raw, numel, dtype, n_threads=2)
         assert_same_bits(b, a, dtype, f"{fmt}->{dtype}")
+
+
+@pytest.mark.parametrize("fmt", ["Q4_0", "Q4_1"])
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+def test_ggml_nibble_order_matches_gguf_py(fmt, dtype):
+    """The opt-in ggml element order is not a reference behaviour; its oracle is pinned to
+    vectors produced by the independent gguf-py package."""
+    import os
+    from conftest import GOLDEN
+    g = np.load(os.path.join(GOLDEN, f"decode_{fmt}_ggml_order.npz"))
+    t = FORMATS[fmt] | np_oracle.GGML_ORDER
+    assert_same_bits(np_oracle.read_tensor(t, g["raw"], int(g["numel"]), dtype), g[dtype], dtype, fmt)
+    assert_same_bits(c_oracle.read_tensor(t, g["raw"], int(g["numel"]), dtype, n_threads=2), g[dtype], dtype, fmt)
+    # same multiset per block as the reference order, different positions
+    ref = np_oracle.decode_f32(FORMATS[fmt], g["raw"], 32 * 8).reshape(8, 32)
+    alt = np_oracle.decode_f32(t, g["raw"], 32 * 8).reshape(8, 32)
+    assert np.array_equal(alt[:, :16].view(np.uint32), ref[:, 0::2].view(np.uint32))
+    assert np.array_equal(alt[:, 16:].view(np.uint32), ref[:, 1::2].view(np.uint32))
+    with pytest.raises(NotImplementedError):
+        np_oracle.decode_f32(FORMATS["Q8_0"] | np_oracle.GGML_ORDER, g["raw"], 32)
