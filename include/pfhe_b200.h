@@ -57,6 +57,18 @@ enum pfhe_status {
     PFHE_ERR_DEVICE_WAIT = -8    /* a decode kernel gave up waiting for its own bulk copy */
 };
 
+/*
+ * Header-parser helper (host only, no CUDA call): walk `count` length-prefixed
+ * strings (u64 length + bytes each) starting at `base`, of which `avail` bytes
+ * are readable.  Fills offsets[i] (from base, of the first byte of string i)
+ * and lengths[i]; returns the number of bytes the array occupies, or
+ * PFHE_ERR_SHORT_SOURCE if it runs past `avail`.  Takes over the per-string
+ * cursor walk of GGUFReader._read_string inside metadata arrays
+ * (gguf_loader.py:236-240, :268-271); decoding stays in Python.
+ */
+int64_t pfhe_scan_string_array(const void *base, int64_t avail, int64_t count,
+                               int64_t *offsets, int64_t *lengths);
+
 /* Library version (major*10000 + minor*100 + patch). */
 int pfhe_version(void);
 

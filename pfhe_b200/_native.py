@@ -24,7 +24,7 @@ TYPE_FLAG_GGML_ORDER = 0x100                 # PFHE_TYPE_FLAG_GGML_ORDER
 
 # Every symbol include/pfhe_b200.h declares.
 EXPORTED_SYMBOLS = (
-    "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes",
+    "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes", "pfhe_scan_string_array",
     "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex", "pfhe_dequant_launch_batch", "pfhe_dequant_launch_batch_ex",
     "pfhe_dequant_from_host_noalloc", "pfhe_device_status", "pfhe_launch_count",
     "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd",
@@ -66,6 +66,8 @@ def lib() -> ctypes.CDLL:
     i32, i64, vp = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p
     L.pfhe_version.restype = i32
     L.pfhe_last_error_string.restype = ctypes.c_char_p
+    L.pfhe_scan_string_array.restype = i64
+    L.pfhe_scan_string_array.argtypes = [vp, i64, i64, vp, vp]
     L.pfhe_tensor_nbytes.restype = i64
     L.pfhe_tensor_nbytes.argtypes = [i32, i64]
     L.pfhe_dequant_launch.restype = i32

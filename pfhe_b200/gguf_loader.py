@@ -348,12 +348,40 @@ class GGUFReader:
                 values = arr.tolist()
                 del arr
                 return values
+            if item_type == GGUF_METADATA_VALUE_TYPE_STRING and count >= 256:
+                return self._read_string_array(count)
             if item_type == GGUF_METADATA_VALUE_TYPE_BOOL:
                 raw = self._mmap[self._cursor:self._cursor + count]
                 self._cursor += count
                 return [b != 0 for b in raw]
             return [self._read_metadata_value(item_type) for _ in range(count)]
         raise ValueError(f"Unknown metadata value type: {value_type}")
+
+    def _read_string_array(self, count: int) -> List[str]:
+        """Large string arrays (vocabularies, merges): the native helper finds the strings,
+        Python decodes them; the result equals ``[self._read_string() for _ in range(count)]``."""
+        if self._view is None:
+            self._view = np.frombuffer(self._mmap, dtype=np.uint8)
+        avail = len(self._mmap) - self._cursor
+        if count * 8 > avail:
+            raise struct.error("metadata array runs past the end of the file")
+        offsets = np.empty(count, dtype=np.int64)
+        lengths = np.empty(count, dtype=np.int64)
+        used = _native.lib().pfhe_scan_string_array(self._view.ctypes.data + self._cursor, avail, count,
+                                                    offsets.ctypes.data, lengths.ctypes.data)
+        if used < 0:
+            raise struct.error("metadata array runs past the end of the file")
+        base = self._cursor
+        region = self._mmap[base:base + used]                       # one copy of the whole array
+        starts = offsets.tolist()
+        ends = (offsets + lengths).tolist()
+        if region.isascii():
+            text = region.decode("ascii")                           # byte offsets are character offsets
+            values = [text[a:b] for a, b in zip(starts, ends)]
+        else:
+            values = [region[a:b].decode("utf-8") for a, b in zip(starts, ends)]
+        self._cursor += used
+        return values
 
     def _parse_header(self) -> None:
         self._cursor = 0

@@ -173,3 +173,37 @@ def test_caller_name_map_matches_reference(golden_dir):
     assert len(expected) > 20
     for gguf_name, want in expected.items():
         assert map_tensor_name(gguf_name) == want, gguf_name
+
+
+def test_large_string_arrays_native_scan(tmp_path, golden_dir):
+    """Vocabulary-sized string arrays go through pfhe_scan_string_array; values must equal a plain
+    per-string read, for ASCII and multi-byte UTF-8, and a cut file must raise instead of reading on."""
+    ascii_toks = [f"tok{i}" for i in range(1000)] + [""]
+    utf8_toks = [("▁é中" * (i % 3)) + str(i) for i in range(700)]
+    small = ["a", "é"]                                    # below the native-scan threshold
+    p = tmp_path / "s.gguf"
+    synth.write_gguf(p, [synth.TensorSpec("w", (32,), gl.GGML_TYPE_F32)],
+                     [("a", "arr:str", ascii_toks), ("u", "arr:str", utf8_toks), ("s", "arr:str", small), ("after", "u32", 7)],
+                     contents={"w": np.arange(32, dtype=np.float32)})
+    with gl.GGUFReader(p) as r:
+        assert r.metadata["a"] == ascii_toks and r.metadata["u"] == utf8_toks and r.metadata["s"] == small
+        assert r.metadata["after"] == 7 and list(r.tensors) == ["w"]
+        assert all(type(x) is str for x in r.metadata["u"])
+    data = p.read_bytes()
+    cut = data[: data.index("tok500".encode()) + 3]
+    q = tmp_path / "cut.gguf"
+    q.write_bytes(cut)
+    with pytest.raises((struct.error, ValueError)):
+        with gl.GGUFReader(q):
+            pass
+    # the C helper directly
+    import ctypes
+    from pfhe_b200 import _native
+    blob = b"".join(struct.pack("<Q", len(s)) + s for s in (b"ab", b"", b"xyz"))
+    offs = (ctypes.c_int64 * 3)()
+    lens = (ctypes.c_int64 * 3)()
+    L = _native.lib()
+    assert L.pfhe_scan_string_array(blob, len(blob), 3, offs, lens) == len(blob)
+    assert list(offs) == [8, 18, 26] and list(lens) == [2, 0, 3]
+    assert L.pfhe_scan_string_array(blob, len(blob) - 1, 3, offs, lens) == _native.ERR_SHORT_SOURCE
+    assert L.pfhe_scan_string_array(blob, len(blob), 4, offs, lens) == _native.ERR_SHORT_SOURCE
