@@ -101,6 +101,7 @@ using FlatFn = void (*)(const uint8_t *, void *, int64_t);
 struct BlockKernels {
     StagedFn staged[2];      // [streaming stores]
     StagedFn staged_out;
+    StagedFn warp_rings[2];
     FlatFn direct[2];
     FlatFn any;
 };
@@ -113,6 +114,7 @@ template <int T, int MID, int OUT> static BlockKernels block_kernels()
 {
     return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
                         dequant_blocks_staged_out<T, MID, OUT>,
+                        {dequant_blocks_warp_rings<T, MID, OUT, false>, dequant_blocks_warp_rings<T, MID, OUT, true>},
                         {dequant_blocks_direct<T, MID, OUT, false>, dequant_blocks_direct<T, MID, OUT, true>},
                         dequant_any_alignment<T, MID, OUT>};
 }
@@ -310,6 +312,26 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
         if (blocks > max_ctas) blocks = max_ctas;
         k.direct[ss]<<<(unsigned)blocks, cfg.threads, 0, stream>>>(src8, dst, n);
         return check_launch(stream, "direct kernel launch");
+    }
+
+    if (variant == 5) {
+        // warp-private rings: tile_blocks is per warp and used exactly
+        BlockKernelArgs w;
+        fill_packed(&w.t, src8, dst, n, bb);
+        w.tile_blocks = cfg.tile_blocks;
+        w.stages = cfg.stages;
+        w.interleaved = 1;
+        if ((rc = status_word(dev, &w.status))) return rc;
+        const int nwarps = cfg.threads / 32;
+        const int64_t tiles = (n_blocks + w.tile_blocks - 1) / w.tile_blocks;
+        int64_t grid = (tiles + nwarps - 1) / nwarps;
+        if (grid > max_ctas) grid = max_ctas;
+        const size_t smem = (size_t)nwarps * w.stages * (w.tile_blocks * bb + 16);
+        if (smem > kSmemBudget) { set_error("tile configuration needs %zu bytes of shared memory", smem); return PFHE_ERR_BAD_ARG; }
+        StagedFn wf = k.warp_rings[ss];
+        if ((rc = ensure_smem(reinterpret_cast<const void *>(wf), dev, smem))) return rc;
+        wf<<<(unsigned)grid, cfg.threads, smem, stream>>>(w);
+        return check_launch(stream, "warp-ring kernel launch");
     }
 
     BlockKernelArgs a;

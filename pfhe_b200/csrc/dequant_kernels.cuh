@@ -575,6 +575,98 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged(const BlockKernelAr
 }
 
 // ---------------------------------------------------------------------------
+// Variant 5: every warp runs its own ring of stages; after set-up there is no
+// CTA-wide barrier.  Tiles (of `tile_blocks` blocks, per warp) are dealt
+// round-robin to all warps of the grid, so the warps of a CTA work on adjacent
+// tiles.
+// ---------------------------------------------------------------------------
+constexpr int kMaxWarps = 16;
+
+template <int T, int MID, int OUT, bool kStream>
+__global__ void __launch_bounds__(512) dequant_blocks_warp_rings(const BlockKernelArgs a)
+{
+    constexpr int BB = Fmt<T>::kBytes;
+    constexpr int VEC = 16 / OutT<OUT>::kSize;
+    constexpr int UPB = 32 / VEC;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full_all[kMaxWarps * kMaxStages];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    const int stage_bytes = a.tile_blocks * BB + 16;
+    uint8_t *ring = smem + (size_t)warp * a.stages * stage_bytes;
+    uint64_t *full = full_all + warp * kMaxStages;
+    if (lane == 0) {
+        for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    const PackedTensor &pt = a.t;
+    const int64_t total_warps = (int64_t)gridDim.x * nwarps;
+    const int64_t first = ((int64_t)blockIdx.x * nwarps + warp) * a.tile_blocks;
+    const int64_t stride = total_warps * a.tile_blocks;
+    const int64_t end = pt.n_blocks;
+    if (first >= end) return;
+    const int n_tiles = (int)((end - first + stride - 1) / stride);
+
+    auto issue = [&](int k) {
+        const int s = k % a.stages;
+        const int64_t tb0 = first + (int64_t)k * stride;
+        const int64_t nb = (end - tb0) < a.tile_blocks ? (end - tb0) : a.tile_blocks;
+        const int64_t off = tb0 * BB;
+        int64_t bytes = (nb * BB + pt.skew + 15) & ~(int64_t)15;
+        if (off + bytes > pt.span_bytes) bytes = pt.span_bytes - off;
+        mbar_expect_tx(&full[s], (uint32_t)bytes);
+        bulk_g2s(ring + (size_t)s * stage_bytes, pt.src16 + off, (uint32_t)bytes, &full[s]);
+    };
+    if (lane == 0) {
+        const int pre = n_tiles < a.stages ? n_tiles : a.stages;
+        for (int k = 0; k < pre; ++k) issue(k);
+    }
+
+    uint32_t parity_bits = 0;
+    int k = 0;
+    for (; k < n_tiles; ++k) {
+        const int s = k % a.stages;
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait_bounded(&full[s], (parity_bits >> s) & 1u, kDeviceWaitLimitNs);
+        if (__any_sync(0xffffffffu, !ok)) break;                  // also orders lane 0's observation before the reads
+        parity_bits ^= 1u << s;
+
+        const uint8_t *tile = ring + (size_t)s * stage_bytes + pt.skew;
+        const int64_t tb0 = first + (int64_t)k * stride;
+        const int nb = (int)((end - tb0) < a.tile_blocks ? (end - tb0) : a.tile_blocks);
+        const int64_t e0 = tb0 << 5;
+        const int64_t rem = pt.n_elements - e0;
+        const int tile_elems = nb << 5;
+        const int valid = rem < tile_elems ? (int)rem : tile_elems;
+        const int full_units = valid / VEC;
+        uint8_t *op = reinterpret_cast<uint8_t *>(pt.dst) + e0 * OutT<OUT>::kSize + (size_t)lane * 16;
+        const uint8_t *bp = tile + (lane / UPB) * BB;
+        const int c = lane % UPB;
+        constexpr int bstep = (32 / UPB) * BB;
+#pragma unroll 4
+        for (int u = lane; u < full_units; u += 32, bp += bstep, op += 512) {
+            const uint4 r = decode_unit<T, MID, OUT, true>(bp, c);
+            store16<kStream>(op, r);
+        }
+        if (valid % VEC != 0 && lane == 0) {
+            for (int e = full_units * VEC; e < valid; ++e)
+                store_scalar<MID, OUT>(pt.dst, e0 + e, decode_element_bytes<T>(tile, e));
+        }
+        __syncwarp();                                             // all lanes done with stage s
+        if (lane == 0 && k + a.stages < n_tiles) issue(k + a.stages);
+    }
+    if (k < n_tiles && lane == 0) {
+        atomicExch(a.status, DEV_WAIT_TIMEOUT);
+        const int last = (k + a.stages) < n_tiles ? (k + a.stages) : n_tiles;
+        for (int j = k; j < last; ++j)
+            (void)mbar_wait_bounded(&full[j % a.stages], (parity_bits >> (j % a.stages)) & 1u, kDeviceWaitLimitNs / 8);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Batch kernel: up to kMaxBatch quantised tensors of mixed formats in ONE
 // launch.  Every tensor is cut into tiles of `tile_blocks` blocks; the tiles of
 // all tensors form one sequence that is dealt round-robin to the CTAs, and each

@@ -171,7 +171,7 @@ class _Stager:
     slot_bytes = 64 << 20
     n_slots = 4
     source = os.environ.get("PFHE_SOURCE", "mmap")   # "mmap": copy out of the mapping; "pread": read the file
-    n_threads = 0          # 0: from PFHE_COPY_THREADS, else half the cores this rank can claim (2..12)
+    n_threads = 0          # 0: from PFHE_COPY_THREADS, else three quarters of the cores this rank can claim (2..16)
 
     @classmethod
     def _copy_threads(cls) -> int:
@@ -185,7 +185,7 @@ class _Stager:
         except AttributeError:
             cores = os.cpu_count() or 4
         ranks_here = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1")))
-        return max(2, min(12, cores // (2 * ranks_here)))
+        return max(2, min(16, (cores * 3 // 4) // ranks_here))
 
     def __init__(self, device_index: int):
         self.device_index = device_index

@@ -23,6 +23,8 @@ VARIANTS = {
     "direct": {"variant": 2},
     "staged_out": {"variant": 3, "tile_blocks": 128, "stages": 3},
     "per_element": {"variant": 9},
+    "warp_rings": {"variant": 5, "tile_blocks": 64, "stages": 2, "threads": 256, "ctas_per_sm": 4},
+    "warp_rings_tiny": {"variant": 5, "tile_blocks": 8, "stages": 3, "threads": 64, "ctas_per_sm": 1},
 }
 
 
@@ -74,7 +76,7 @@ def test_ragged_and_tiny_sizes(fmt, numel):
     raw = synth.random_packed(t, numel, np.random.default_rng(numel))
     for dtype in OUT_DTYPES:
         want = np_oracle.read_tensor(t, raw, numel, dtype)
-        for variant in ("default", "direct", "staged_out", "staged_small_tiles"):
+        for variant in ("default", "direct", "staged_out", "staged_small_tiles", "warp_rings", "warp_rings_tiny"):
             got = decode_on_gpu(t, raw, numel, dtype, cfg=VARIANTS[variant])
             assert_same_bits(to_bits(got), want, dtype, f"{fmt} n={numel}->{dtype} [{variant}]")
 
@@ -88,7 +90,7 @@ def test_unaligned_source(fmt, skew):
     raw = synth.random_packed(t, numel, np.random.default_rng(skew))
     for dtype in ("f16", "f32"):
         want = np_oracle.read_tensor(t, raw, numel, dtype)
-        for variant in ("default", "staged_out", "staged_small_tiles"):
+        for variant in ("default", "staged_out", "staged_small_tiles", "warp_rings"):
             got = decode_on_gpu(t, raw, numel, dtype, skew=skew, cfg=VARIANTS[variant])
             assert_same_bits(to_bits(got), want, dtype, f"{fmt} skew={skew}->{dtype} [{variant}]")
 
