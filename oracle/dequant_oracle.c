@@ -13,6 +13,7 @@
  * All IEEE conversions are done with integer arithmetic so that the result
  * does not depend on compiler flags, x87/SSE modes or _Float16 support.
  */
+#include <math.h>
 #include <stdint.h>
 #include <string.h>
 
@@ -27,7 +28,17 @@ enum {
     ORACLE_Q4_0 = 2,
     ORACLE_Q4_1 = 3,
     ORACLE_Q8_0 = 8,
-    ORACLE_BF16 = 30
+    ORACLE_BF16 = 30,
+    /* Formats the reference names (gguf_loader.py:37-46) but cannot decode.  Restated from ggml's
+     * published dequantize_row_q5_0 / q5_1 / q2_K / q3_K / q4_K / q5_K / q6_K; pinned against the
+     * gguf-py package's dequantize() (tests/golden/decode_<type>_ggml.npz), not against the reference. */
+    ORACLE_Q5_0 = 6,
+    ORACLE_Q5_1 = 7,
+    ORACLE_Q2_K = 10,
+    ORACLE_Q3_K = 11,
+    ORACLE_Q4_K = 12,
+    ORACLE_Q5_K = 13,
+    ORACLE_Q6_K = 14
 };
 
 /* OR-ed into Q4_0 / Q4_1: ggml's own element order (ggml-quants.c dequantize_row_q4_0 /
@@ -42,7 +53,8 @@ static int block_elems(int t)
 {
     switch (t & ~ORACLE_GGML_ORDER) {
     case ORACLE_F32: case ORACLE_F16: case ORACLE_BF16: return 1;
-    case ORACLE_Q4_0: case ORACLE_Q4_1: case ORACLE_Q8_0: return 32;
+    case ORACLE_Q4_0: case ORACLE_Q4_1: case ORACLE_Q8_0: case ORACLE_Q5_0: case ORACLE_Q5_1: return 32;
+    case ORACLE_Q2_K: case ORACLE_Q3_K: case ORACLE_Q4_K: case ORACLE_Q5_K: case ORACLE_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -55,6 +67,13 @@ static int block_bytes(int t)
     case ORACLE_Q4_0: return 18;
     case ORACLE_Q4_1: return 20;
     case ORACLE_Q8_0: return 34;
+    case ORACLE_Q5_0: return 22;
+    case ORACLE_Q5_1: return 24;
+    case ORACLE_Q2_K: return 84;
+    case ORACLE_Q3_K: return 110;
+    case ORACLE_Q4_K: return 144;
+    case ORACLE_Q5_K: return 176;
+    case ORACLE_Q6_K: return 210;
     default: return 0;
     }
 }
@@ -169,6 +188,67 @@ static void decode_block(int t, const uint8_t *b, float *v)
     }
 }
 
+/* 6-bit scale and minimum of sub-block j of a Q4_K / Q5_K block (12 packed bytes at s). */
+static void k4_scale_min(const uint8_t *s, int j, int *sc, int *mn)
+{
+    if (j < 4) { *sc = s[j] & 63; *mn = s[j + 4] & 63; }
+    else { *sc = (s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4); *mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4); }
+}
+
+/* Element k of one Q5_0 / Q5_1 / K-quant block.  All products before the last operation are
+ * exact in float (fp16 scale x small integers), so fmaf / one multiply gives the single rounding
+ * that ggml's float code and gguf-py's float32 NumPy code both produce. */
+static float extra_element(int t, const uint8_t *b, int k)
+{
+    if (t == ORACLE_Q5_0 || t == ORACLE_Q5_1) {
+        int o = (t == ORACLE_Q5_0) ? 2 : 4;
+        uint32_t qh = (uint32_t)b[o] | ((uint32_t)b[o + 1] << 8) | ((uint32_t)b[o + 2] << 16) | ((uint32_t)b[o + 3] << 24);
+        int byte = b[o + 4 + (k & 15)];
+        int q = ((k & 16) ? (byte >> 4) : (byte & 15)) | (int)(((qh >> k) & 1u) << 4);
+        float d = half_to_f32(rd_u16(b));
+        if (t == ORACLE_Q5_0) return d * (float)(q - 16);
+        return fmaf(d, (float)q, half_to_f32(rd_u16(b + 2)));
+    }
+    int sb = k >> 5, l = k & 31;
+    if (t == ORACLE_Q4_K || t == ORACLE_Q5_K) {
+        int sc, mn;
+        k4_scale_min(b + 4, sb, &sc, &mn);
+        int byte = b[(t == ORACLE_Q4_K ? 16 : 48) + 32 * (sb >> 1) + l];
+        int q = (sb & 1) ? (byte >> 4) : (byte & 15);
+        if (t == ORACLE_Q5_K) q |= ((b[16 + l] >> sb) & 1) << 4;
+        float dl = half_to_f32(rd_u16(b)) * (float)sc;
+        float ml = half_to_f32(rd_u16(b + 2)) * (float)mn;
+        return fmaf(dl, (float)q, -ml);
+    }
+    if (t == ORACLE_Q6_K) {
+        int half = sb >> 2, r = sb & 3;
+        int lo = b[64 * half + 32 * (r & 1) + l], hi = b[128 + 32 * half + l];
+        int q = (((r >> 1) ? (lo >> 4) : (lo & 15)) | (((hi >> (2 * r)) & 3) << 4)) - 32;
+        float dl = half_to_f32(rd_u16(b + 208)) * (float)(int8_t)b[192 + (k >> 4)];
+        return dl * (float)q;
+    }
+    int half = k >> 7, r = (k >> 5) & 3;
+    if (t == ORACLE_Q2_K) {
+        int q = (b[16 + 32 * half + l] >> (2 * r)) & 3;
+        int s = b[k >> 4];
+        float dl = half_to_f32(rd_u16(b + 80)) * (float)(s & 15);
+        float ml = half_to_f32(rd_u16(b + 82)) * (float)(s >> 4);
+        return fmaf(dl, (float)q, -ml);
+    }
+    /* ORACLE_Q3_K */
+    int j = k >> 4;
+    int q = (((b[32 + 32 * half + l] >> (2 * r)) & 3) | (((b[l] >> sb) & 1) << 2)) - 4;
+    int low = (j < 8) ? (b[96 + j] & 15) : (b[96 + j - 8] >> 4);
+    int high = (b[104 + (j & 3)] >> (2 * (j >> 2))) & 3;
+    float dl = half_to_f32(rd_u16(b + 108)) * (float)((low | (high << 4)) - 32);
+    return dl * (float)q;
+}
+
+static int is_extra(int t)
+{
+    return t == ORACLE_Q5_0 || t == ORACLE_Q5_1 || (t >= ORACLE_Q2_K && t <= ORACLE_Q6_K);
+}
+
 /*
  * Decode `numel` elements of ggml type `ggml_type` from `src` into float32.
  * Returns 0, -1 for an unsupported type, -2 when src_bytes is shorter than
@@ -200,6 +280,13 @@ int oracle_decode_f32(int ggml_type, const uint8_t *src, int64_t src_bytes,
 #pragma omp parallel for num_threads(n_threads) schedule(static)
         for (int64_t i = 0; i < numel; i++)
             out[i] = bits_to_f32((uint32_t)rd_u16(src + 2 * i) << 16);
+        return 0;
+    }
+    if (is_extra(ggml_type)) {
+        int be = block_elems(ggml_type), xb = block_bytes(ggml_type);
+#pragma omp parallel for num_threads(n_threads) schedule(static)
+        for (int64_t i = 0; i < numel; i++)
+            out[i] = extra_element(ggml_type, src + (i / be) * xb, (int)(i % be));
         return 0;
     }
     int bb = block_bytes(ggml_type);

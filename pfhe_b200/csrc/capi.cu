@@ -124,6 +124,22 @@ template <int T, int MID, int OUT> static ElemKernels elem_kernels()
                        dequant_any_alignment<T, MID, OUT>};
 }
 
+// The formats beyond the reference's six get the main kernel and the fallback only.
+template <int T, int MID, int OUT> static BlockKernels extra_kernels()
+{
+    return BlockKernels{{dequant_blocks_staged<T, MID, OUT, true>, dequant_blocks_staged<T, MID, OUT, true>},
+                        nullptr, {nullptr, nullptr}, {nullptr, nullptr}, dequant_any_alignment<T, MID, OUT>};
+}
+template <int T> static bool pick_extra(int mid, int out, BlockKernels *k)
+{
+#define PFHE_CASE(M, O) if (mid == M && out == O) { *k = extra_kernels<T, M, O>(); return true; }
+    PFHE_CASE(O_F32, O_F32) PFHE_CASE(O_F32, O_F16) PFHE_CASE(O_F32, O_BF16)
+    PFHE_CASE(O_F16, O_F32) PFHE_CASE(O_F16, O_F16) PFHE_CASE(O_F16, O_BF16)
+    PFHE_CASE(O_BF16, O_F32) PFHE_CASE(O_BF16, O_F16) PFHE_CASE(O_BF16, O_BF16)
+#undef PFHE_CASE
+    return false;
+}
+
 template <int T> static bool pick_block(int mid, int out, BlockKernels *k)
 {
 #define PFHE_CASE(M, O) if (mid == M && out == O) { *k = block_kernels<T, M, O>(); return true; }
@@ -151,8 +167,15 @@ int type_geometry(int t, int *elems, int *bytes)
     case T_Q4_0: case T_Q4_0G: *elems = 32; *bytes = 18; return PFHE_OK;
     case T_Q4_1: case T_Q4_1G: *elems = 32; *bytes = 20; return PFHE_OK;
     case T_Q8_0: *elems = 32; *bytes = 34; return PFHE_OK;
+    case T_Q5_0: *elems = 32; *bytes = 22; return PFHE_OK;
+    case T_Q5_1: *elems = 32; *bytes = 24; return PFHE_OK;
+    case T_Q2_K: *elems = 256; *bytes = 84; return PFHE_OK;
+    case T_Q3_K: *elems = 256; *bytes = 110; return PFHE_OK;
+    case T_Q4_K: *elems = 256; *bytes = 144; return PFHE_OK;
+    case T_Q5_K: *elems = 256; *bytes = 176; return PFHE_OK;
+    case T_Q6_K: *elems = 256; *bytes = 210; return PFHE_OK;
     default:
-        set_error("ggml type %d is not one of F32, F16, BF16, Q4_0, Q4_1, Q8_0", t);
+        set_error("ggml type %d is not one of F32, F16, BF16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K..Q6_K", t);
         return PFHE_ERR_BAD_TYPE;
     }
 }
@@ -201,6 +224,8 @@ struct Shape { int tile_blocks, stages, threads, ctas_per_sm; };
 
 static Shape default_shape(int ggml_type, int out_dtype)
 {
+    if (ggml_type >= T_Q2_K && ggml_type <= T_Q6_K)                 // 256-element blocks: same 32 KB output tile
+        return out_dtype == O_F32 ? Shape{32, 2, 256, 2} : Shape{64, 2, 256, 2};
     if (out_dtype == O_F32) return Shape{256, 2, 256, 2};
     if (ggml_type == T_Q8_0) return Shape{256, 2, 256, 3};
     return Shape{512, 2, 256, 2};
@@ -217,14 +242,14 @@ static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
     if (c->streaming_stores < 0) c->streaming_stores = 1;
 }
 
-static void fill_packed(PackedTensor *t, const uint8_t *src, void *dst, int64_t n, int block_bytes)
+static void fill_packed(PackedTensor *t, const uint8_t *src, void *dst, int64_t n, int block_bytes, int block_elems = 32)
 {
     const uintptr_t s = reinterpret_cast<uintptr_t>(src);
     t->skew = (int)(s & 15);
     t->src16 = src - t->skew;
     t->dst = dst;
     t->n_elements = n;
-    t->n_blocks = (n + 31) / 32;
+    t->n_blocks = (n + block_elems - 1) / block_elems;
     t->span_bytes = (t->skew + t->n_blocks * block_bytes + 15) & ~(int64_t)15;
     t->kind = 0;
 }
@@ -287,17 +312,30 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
 
     BlockKernels k;
     bool ok = false;
-    if (ggml_type == T_Q4_0) ok = pick_block<T_Q4_0>(mid, out, &k);
+    if (ggml_type == T_Q5_0) ok = pick_extra<T_Q5_0>(mid, out, &k);
+    else if (ggml_type == T_Q5_1) ok = pick_extra<T_Q5_1>(mid, out, &k);
+    else if (ggml_type == T_Q2_K) ok = pick_extra<T_Q2_K>(mid, out, &k);
+    else if (ggml_type == T_Q3_K) ok = pick_extra<T_Q3_K>(mid, out, &k);
+    else if (ggml_type == T_Q4_K) ok = pick_extra<T_Q4_K>(mid, out, &k);
+    else if (ggml_type == T_Q5_K) ok = pick_extra<T_Q5_K>(mid, out, &k);
+    else if (ggml_type == T_Q6_K) ok = pick_extra<T_Q6_K>(mid, out, &k);
+    else if (ggml_type == T_Q4_0) ok = pick_block<T_Q4_0>(mid, out, &k);
     else if (ggml_type == T_Q4_1) ok = pick_block<T_Q4_1>(mid, out, &k);
     else if (ggml_type == T_Q4_0G) ok = pick_block<T_Q4_0G>(mid, out, &k);
     else if (ggml_type == T_Q4_1G) ok = pick_block<T_Q4_1G>(mid, out, &k);
     else ok = pick_block<T_Q8_0>(mid, out, &k);
     if (!ok) { set_error("no kernel"); return PFHE_ERR_BAD_DTYPE; }
 
-    const int64_t n_blocks = (n + 31) / 32;
+    const int64_t n_blocks = (n + be - 1) / be;
     int variant = cfg.variant;
     if ((s % 2) || (d % 16)) variant = 9;                           // odd source or unaligned destination
 
+    if ((variant == 2 && !k.direct[ss]) || (variant == 3 && !k.staged_out) || (variant == 5 && !k.warp_rings[ss])) {
+        set_error("kernel variant %d is not built for ggml type %d", variant, ggml_type);
+        return PFHE_ERR_BAD_ARG;
+    }
+    const int upb_max = be / 4;                                      // units per block when the output is fp32
+    if (cfg.threads % (upb_max > 32 ? upb_max : 32)) { set_error("threads must be a multiple of %d for this type", upb_max); return PFHE_ERR_BAD_ARG; }
     if (variant == 9) {
         int64_t blocks = (n + 255) / 256;
         if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
@@ -317,7 +355,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     if (variant == 5) {
         // warp-private rings: tile_blocks is per warp and used exactly
         BlockKernelArgs w;
-        fill_packed(&w.t, src8, dst, n, bb);
+        fill_packed(&w.t, src8, dst, n, bb, be);
         w.tile_blocks = cfg.tile_blocks;
         w.stages = cfg.stages;
         w.interleaved = 1;
@@ -335,7 +373,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     }
 
     BlockKernelArgs a;
-    fill_packed(&a.t, src8, dst, n, bb);
+    fill_packed(&a.t, src8, dst, n, bb, be);
     a.tile_blocks = cfg.tile_blocks;
     a.stages = cfg.stages;
     a.interleaved = cfg.reserved[0] == 1 ? 0 : 1;
@@ -346,7 +384,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
     if (cfg.reserved[1] == 0) {
         // Tiles near the requested length that fill whole rounds of the grid.
-        const int out_per_block = variant == 3 ? 2 * 32 * osz : 0;
+        const int out_per_block = variant == 3 ? 2 * be * osz : 0;
         const size_t per_cta = kSmemBudget / (size_t)(cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 1) - 1024;
         int max_tile = (int)(per_cta / ((size_t)a.stages * bb + out_per_block) - 16) / 8 * 8;
         if (max_tile > 2048) max_tile = 2048;
@@ -363,7 +401,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     size_t smem = (size_t)a.stages * (a.tile_blocks * bb + 16);
     StagedFn fn = k.staged[ss];
     if (variant == 3) {
-        smem = ((smem + 127) & ~(size_t)127) + 2 * (size_t)a.tile_blocks * 32 * osz;
+        smem = ((smem + 127) & ~(size_t)127) + 2 * (size_t)a.tile_blocks * be * osz;
         fn = k.staged_out;
     }
     if (smem > kSmemBudget) { set_error("tile configuration needs %zu bytes of shared memory", smem); return PFHE_ERR_BAD_ARG; }
@@ -456,7 +494,9 @@ int launch_batch(const pfhe_tensor_desc *d, int n, cudaStream_t stream, const pf
         if (t.n_elements == 0) continue;
         int be = 0, bb = 0;
         type_geometry(t.ggml_type, &be, &bb);
-        const bool batchable = be == 32 && reinterpret_cast<uintptr_t>(t.src_dev) % 2 == 0 &&
+        const int base_type = t.ggml_type & ~T_ORDER_FLAG;
+        const bool batchable = (base_type == T_Q4_0 || base_type == T_Q4_1 || base_type == T_Q8_0) &&
+                               reinterpret_cast<uintptr_t>(t.src_dev) % 2 == 0 &&
                                reinterpret_cast<uintptr_t>(t.dst_dev) % 16 == 0;
         if (!batchable) {
             rc = launch_decode(t.ggml_type, t.out_dtype, t.out_dtype, t.src_dev, t.src_bytes, t.dst_dev, t.dst_bytes,

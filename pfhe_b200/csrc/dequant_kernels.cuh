@@ -137,6 +137,10 @@ __device__ __forceinline__ uint32_t h2_sub_mul(uint32_t x, uint32_t c, uint32_t 
     return *reinterpret_cast<uint32_t *>(&r);
 }
 
+}  // namespace pfhe
+#include "ggml_extra_formats.cuh"
+namespace pfhe {
+
 // ---------------------------------------------------------------------------
 // Sixteen output bytes ("unit") of a quantised tensor.
 // VEC = 8 outputs for 16-bit targets, 4 for fp32.  `blk` points at the start of
@@ -146,7 +150,9 @@ template <int T, int MID, int OUT, bool kShared>
 __device__ __forceinline__ uint4 decode_unit(const uint8_t *blk, int c)
 {
     uint4 r;
-    if constexpr (T == T_Q4_0G || T == T_Q4_1G) {
+    if constexpr (IsExtra<T>::value) {
+        return extra_unit<T, MID, OUT>(blk, c);
+    } else if constexpr (T == T_Q4_0G || T == T_Q4_1G) {
         // ggml order: a unit takes either the low or the high nibbles of a run of bytes.
         constexpr bool kHasMin = (T == T_Q4_1G);
         constexpr int kQs = kHasMin ? 4 : 2;
@@ -307,6 +313,8 @@ template <int T> __device__ __forceinline__ float decode_element_bytes(const uin
     } else if constexpr (T == T_BF16) {
         const uint8_t *p = src + 2 * i;
         return bf16_bits_to_f32((uint32_t)p[0] | ((uint32_t)p[1] << 8));
+    } else if constexpr (IsExtra<T>::value) {
+        return extra_element<T>(src + (i / Fmt<T>::kElems) * Fmt<T>::kBytes, (int)(i % Fmt<T>::kElems));
     } else {
         const uint8_t *b = src + (i >> 5) * Fmt<T>::kBytes;
         const int k = (int)(i & 31);
@@ -415,7 +423,7 @@ struct PackedTensor {
     const uint8_t *src16;   // source rounded down to a 16-byte line
     void *dst;              // 16-byte aligned
     int64_t n_elements;
-    int64_t n_blocks;       // ceil(n_elements / 32)
+    int64_t n_blocks;       // ceil(n_elements / elements per block)
     int64_t span_bytes;     // bytes from src16 to the 16-byte-rounded end of the packed data
     int32_t skew;           // src - src16 (even, 0..14)
     int32_t kind;           // batch kernel only: ggml type * 4 + output dtype
@@ -447,10 +455,10 @@ __device__ __forceinline__ void decode_tile(const PackedTensor &pt, int64_t tb0,
 {
     constexpr int BB = Fmt<T>::kBytes;
     constexpr int VEC = 16 / OutT<OUT>::kSize;       // outputs per 16-byte store
-    constexpr int UPB = 32 / VEC;                    // units per block
-    const int64_t e0 = tb0 << 5;
+    constexpr int UPB = Fmt<T>::kElems / VEC;        // units per block
+    const int64_t e0 = tb0 * Fmt<T>::kElems;
     const int64_t rem = pt.n_elements - e0;                        // > 0
-    const int tile_elems = nb << 5;
+    const int tile_elems = nb * Fmt<T>::kElems;
     const int valid = rem < tile_elems ? (int)rem : tile_elems;
     const int full_units = valid / VEC;
     uint8_t *out = reinterpret_cast<uint8_t *>(pt.dst) + e0 * OutT<OUT>::kSize;
@@ -587,7 +595,7 @@ __global__ void __launch_bounds__(512) dequant_blocks_warp_rings(const BlockKern
 {
     constexpr int BB = Fmt<T>::kBytes;
     constexpr int VEC = 16 / OutT<OUT>::kSize;
-    constexpr int UPB = 32 / VEC;
+    constexpr int UPB = Fmt<T>::kElems / VEC;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_all[kMaxWarps * kMaxStages];
 
@@ -637,15 +645,15 @@ __global__ void __launch_bounds__(512) dequant_blocks_warp_rings(const BlockKern
         const uint8_t *tile = ring + (size_t)s * stage_bytes + pt.skew;
         const int64_t tb0 = first + (int64_t)k * stride;
         const int nb = (int)((end - tb0) < a.tile_blocks ? (end - tb0) : a.tile_blocks);
-        const int64_t e0 = tb0 << 5;
+        const int64_t e0 = tb0 * Fmt<T>::kElems;
         const int64_t rem = pt.n_elements - e0;
-        const int tile_elems = nb << 5;
+        const int tile_elems = nb * Fmt<T>::kElems;
         const int valid = rem < tile_elems ? (int)rem : tile_elems;
         const int full_units = valid / VEC;
         uint8_t *op = reinterpret_cast<uint8_t *>(pt.dst) + e0 * OutT<OUT>::kSize + (size_t)lane * 16;
         const uint8_t *bp = tile + (lane / UPB) * BB;
         const int c = lane % UPB;
-        constexpr int bstep = (32 / UPB) * BB;
+        constexpr int bstep = (UPB >= 32 ? 1 : 32 / UPB) * BB;
 #pragma unroll 4
         for (int u = lane; u < full_units; u += 32, bp += bstep, op += 512) {
             const uint4 r = decode_unit<T, MID, OUT, true>(bp, c);
@@ -775,12 +783,12 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKern
 {
     constexpr int BB = Fmt<T>::kBytes;
     constexpr int VEC = 16 / OutT<OUT>::kSize;
-    constexpr int UPB = 32 / VEC;
+    constexpr int UPB = Fmt<T>::kElems / VEC;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full[kMaxStages];
 
     const int stage_bytes = a.tile_blocks * BB + 16;
-    const int out_tile_bytes = a.tile_blocks * 32 * OutT<OUT>::kSize;
+    const int out_tile_bytes = a.tile_blocks * Fmt<T>::kElems * OutT<OUT>::kSize;
     uint8_t *out_smem = smem + (((size_t)a.stages * stage_bytes + 127) & ~(size_t)127);   // two buffers
     const int64_t n_groups = (a.t.n_blocks + 7) >> 3;
     const int64_t g0 = n_groups * blockIdx.x / gridDim.x;
@@ -826,9 +834,9 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKern
         uint8_t *obuf = out_smem + (size_t)(t & 1) * out_tile_bytes;
         const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
         const int nb = (int)((b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks);
-        const int64_t e0 = tb0 << 5;
+        const int64_t e0 = tb0 * Fmt<T>::kElems;
         const int64_t rem = a.t.n_elements - e0;
-        const int tile_elems = nb << 5;
+        const int tile_elems = nb * Fmt<T>::kElems;
         const int valid = rem < tile_elems ? (int)rem : tile_elems;
         const int full_units = valid / VEC;
         uint8_t *gout = reinterpret_cast<uint8_t *>(a.t.dst) + e0 * OutT<OUT>::kSize;
@@ -884,7 +892,7 @@ __global__ void __launch_bounds__(512) dequant_blocks_direct(const uint8_t *__re
 {
     constexpr int BB = Fmt<T>::kBytes;
     constexpr int VEC = 16 / OutT<OUT>::kSize;
-    constexpr int UPB = 32 / VEC;
+    constexpr int UPB = Fmt<T>::kElems / VEC;
     const int64_t full_units = n_elements / VEC;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     uint8_t *out = reinterpret_cast<uint8_t *>(dst);

@@ -199,7 +199,7 @@ int submit_impl(pfhe_loader *ld, const Source &src, int64_t src_bytes, int ggml_
     // Chunks hold whole 8-block groups (block formats) or multiples of 16
     // elements, so every chunk starts on a 16-byte line on both sides.
     int64_t chunk_elems;
-    if (be == 32) chunk_elems = ld->slot_bytes / (8 * bb) * 8 * 32;
+    if (be > 1) chunk_elems = ld->slot_bytes / (8 * bb) * 8 * be;
     else chunk_elems = ld->slot_bytes / bb / 16 * 16;
     if (chunk_elems <= 0) { set_error("slot too small"); return PFHE_ERR_BAD_ARG; }
 

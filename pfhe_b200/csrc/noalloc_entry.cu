@@ -63,7 +63,7 @@ void launch_blocks(const uint8_t *src, void *dst, int64_t n, int *status, int sm
     a.t.skew = 0;
     a.t.dst = dst;
     a.t.n_elements = n;
-    a.t.n_blocks = (n + 31) / 32;
+    a.t.n_blocks = (n + Fmt<T>::kElems - 1) / Fmt<T>::kElems;
     a.t.span_bytes = (a.t.n_blocks * Fmt<T>::kBytes + 15) & ~(int64_t)15;
     a.t.kind = 0;
     a.stages = 2;
@@ -73,7 +73,7 @@ void launch_blocks(const uint8_t *src, void *dst, int64_t n, int *status, int sm
     const int64_t max_ctas = (int64_t)sms * 2;
     const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
     const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
-    const int target = OUT == O_F32 ? 256 : 512;               // 34.8 KB of shared memory at most: no opt-in needed
+    const int target = (OUT == O_F32 ? 8192 : 16384) / Fmt<T>::kElems;   // 34.8 KB of shared memory at most: no opt-in needed
     a.tile_blocks = groups_per_cta * 8 < target ? (int)(groups_per_cta * 8) : target;
     const size_t smem = (size_t)a.stages * (a.tile_blocks * Fmt<T>::kBytes + 16);
     dequant_blocks_staged<T, OUT, OUT, true><<<(unsigned)grid, 256, smem, stream>>>(a);
@@ -103,7 +103,7 @@ void dispatch_out(int out, const uint8_t *src, void *dst, int64_t n, int *status
     const bool aligned = reinterpret_cast<uintptr_t>(dst) % 16 == 0;
 #define PFHE_GO(O)                                                                   \
     if (!aligned) launch_any<T, O>(src, dst, n, sms, stream);                        \
-    else if constexpr (Fmt<T>::kElems == 32) launch_blocks<T, O>(src, dst, n, status, sms, stream); \
+    else if constexpr (Fmt<T>::kElems > 1) launch_blocks<T, O>(src, dst, n, status, sms, stream); \
     else launch_elements<T, O>(src, dst, n, sms, stream);
     if (out == O_F32) { PFHE_GO(O_F32) }
     else if (out == O_F16) { PFHE_GO(O_F16) }
@@ -158,7 +158,15 @@ extern "C" int pfhe_dequant_from_host_noalloc(int ggml_type, int out_dtype, cons
     case T_Q8_0: dispatch_out<T_Q8_0>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
     case T_F16: dispatch_out<T_F16>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
     case T_BF16: dispatch_out<T_BF16>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
-    default: dispatch_out<T_F32>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q5_0: dispatch_out<T_Q5_0>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q5_1: dispatch_out<T_Q5_1>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q2_K: dispatch_out<T_Q2_K>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q3_K: dispatch_out<T_Q3_K>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q4_K: dispatch_out<T_Q4_K>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q5_K: dispatch_out<T_Q5_K>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_Q6_K: dispatch_out<T_Q6_K>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    case T_F32: dispatch_out<T_F32>(out_dtype, src, dst_dev, n_elements, status, sms, stream); break;
+    default: set_error("ggml type %d has no no-alloc kernel", ggml_type); return PFHE_ERR_BAD_TYPE;
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "no-alloc decode launch");

@@ -62,6 +62,9 @@ GGML_TYPE_BF16 = 30
 QK4_0 = QK4_1 = QK5_0 = QK5_1 = QK8_0 = QK8_1 = 32
 
 # ggml type -> (elements per block, bytes per block); the kernels' contract.
+# The first six are the reference's table (:57-65).  The rest are formats the reference names
+# (:37-46) but cannot decode -- there its ``nbytes`` raises ValueError; here they decode with
+# ggml's published arithmetic and element order.
 QUANT_INFO = {
     GGML_TYPE_F32: (1, 4),
     GGML_TYPE_F16: (1, 2),
@@ -69,7 +72,15 @@ QUANT_INFO = {
     GGML_TYPE_Q4_0: (32, 18),
     GGML_TYPE_Q4_1: (32, 20),
     GGML_TYPE_Q8_0: (32, 34),
+    GGML_TYPE_Q5_0: (32, 22),
+    GGML_TYPE_Q5_1: (32, 24),
+    GGML_TYPE_Q2_K: (256, 84),
+    GGML_TYPE_Q3_K: (256, 110),
+    GGML_TYPE_Q4_K: (256, 144),
+    GGML_TYPE_Q5_K: (256, 176),
+    GGML_TYPE_Q6_K: (256, 210),
 }
+REFERENCE_TYPES = (GGML_TYPE_F32, GGML_TYPE_F16, GGML_TYPE_BF16, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0)
 
 GGUF_TYPE_NAMES = {
     GGML_TYPE_F32: "F32", GGML_TYPE_F16: "F16", GGML_TYPE_BF16: "BF16",

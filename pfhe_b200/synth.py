@@ -48,6 +48,8 @@ def random_packed(ggml_type: int, numel: int, rng: np.random.Generator, scale: O
         if ggml_type == GGML_TYPE_F16:
             return vals.astype(np.float16).view(np.uint8)
         return (vals.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8)   # truncated bf16 is fine for inputs
+    if ggml_type not in (GGML_TYPE_Q8_0, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1):
+        return _random_extra(ggml_type, n_blocks, block_bytes, rng).reshape(-1)
     out = np.empty((n_blocks, block_bytes), dtype=np.uint8)
     if ggml_type == GGML_TYPE_Q8_0:
         s = 0.01 if scale is None else scale
@@ -62,6 +64,19 @@ def random_packed(ggml_type: int, numel: int, rng: np.random.Generator, scale: O
             qs = 4
         out[:, qs:] = rng.integers(0, 256, size=(n_blocks, 16), dtype=np.uint8)
     return out.reshape(-1)
+
+
+# byte offsets of the fp16 fields (scale d, and minimum m / dmin) in the formats beyond the reference's six
+_F16_FIELDS = {6: (0,), 7: (0, 2), 10: (80, 82), 11: (108,), 12: (0, 2), 13: (0, 2), 14: (208,)}
+
+
+def _random_extra(ggml_type: int, n_blocks: int, block_bytes: int, rng: np.random.Generator) -> np.ndarray:
+    """Q5_0, Q5_1 and K-quant blocks: uniform random payload bytes, |N(0,1)|*0.02-like fp16 scales."""
+    out = rng.integers(0, 256, size=(n_blocks, block_bytes), dtype=np.uint8)
+    for k, off in enumerate(_F16_FIELDS[ggml_type]):
+        vals = np.abs(rng.standard_normal(n_blocks, dtype=np.float32)) * (0.002 if k == 0 else 0.001)
+        out[:, off:off + 2] = vals.astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+    return out
 
 
 # ---------------------------------------------------------------------------

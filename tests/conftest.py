@@ -12,6 +12,8 @@ GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 F32, F16, Q4_0, Q4_1, Q8_0, BF16 = 0, 1, 2, 3, 8, 30
 FORMATS = {"Q4_0": Q4_0, "Q4_1": Q4_1, "Q8_0": Q8_0, "F16": F16, "BF16": BF16, "F32": F32}
+# formats the reference cannot decode; oracle pinned to gguf-py vectors (decode_<name>_ggml.npz)
+EXTRA_FORMATS = {"Q5_0": 6, "Q5_1": 7, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
 OUT_DTYPES = ("f32", "f16", "bf16")
 CAST2 = (("f16", "bf16"), ("bf16", "f16"), ("f16", "f32"), ("bf16", "f32"))
 
@@ -22,6 +24,10 @@ def pytest_configure(config):
 
 def load_golden(fmt_name: str):
     return np.load(os.path.join(GOLDEN, f"decode_{fmt_name}.npz"))
+
+
+def load_golden_extra(fmt_name: str):
+    return np.load(os.path.join(GOLDEN, f"decode_{fmt_name}_ggml.npz"))
 
 
 def as_bits(a: np.ndarray) -> np.ndarray:

@@ -18,6 +18,7 @@ Files written:
   mini_tensors.npz   reference read_tensor(...) of every tensor in mini.gguf
   decode_Q4_x_ggml_order.npz  the same packed inputs decoded in ggml's own nibble order by the gguf-py
                      package (an independent implementation; the reference has no such mode)
+  decode_<Q5_0|Q5_1|Q2_K..Q6_K>_ggml.npz  formats the reference cannot decode, decoded by gguf-py
   name_map.json      GGUFModel._map_tensor_name(...) of the reference for a list of tensor names
 """
 from __future__ import annotations
@@ -130,8 +131,36 @@ def main(ref_root: str) -> None:
                                 f32=bits(v), f16=bits(v.to(torch.float16)), bf16=bits(v.to(torch.bfloat16)),
                                 source=np.array(f"gguf-py {getattr(gguf, '__version__', '0.19.0')} quants.dequantize"))
             print(NAMES[fmt], "ggml order", n_blocks, "blocks")
+        # --- formats the reference cannot decode at all: Q5_0, Q5_1, K-quants, pinned to gguf-py ------
+        from pfhe_b200 import synth
+        rng2 = np.random.default_rng(777)
+        extra = {"Q5_0": (6, gguf.GGMLQuantizationType.Q5_0, 32, 22), "Q5_1": (7, gguf.GGMLQuantizationType.Q5_1, 32, 24),
+                 "Q2_K": (10, gguf.GGMLQuantizationType.Q2_K, 256, 84), "Q3_K": (11, gguf.GGMLQuantizationType.Q3_K, 256, 110),
+                 "Q4_K": (12, gguf.GGMLQuantizationType.Q4_K, 256, 144), "Q5_K": (13, gguf.GGMLQuantizationType.Q5_K, 256, 176),
+                 "Q6_K": (14, gguf.GGMLQuantizationType.Q6_K, 256, 210)}
+        for name, (tid, gtype, be, bb) in extra.items():
+            n_blocks = 96 if be == 32 else 40
+            blocks = rng2.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+            for off in synth._F16_FIELDS[tid]:                      # any finite fp16 bit pattern as scale / minimum
+                h = rng2.integers(0, 1 << 16, n_blocks, dtype=np.uint16)
+                h = np.where((h & 0x7C00) == 0x7C00, h & 0xBFFF, h).astype(np.uint16)
+                h[: len(SPECIAL_F16) - 3] = np.array([x for x in SPECIAL_F16 if (x & 0x7C00) != 0x7C00], dtype=np.uint16)[: len(SPECIAL_F16) - 3]
+                blocks[:, off:off + 2] = h.view(np.uint8).reshape(n_blocks, 2)
+            blocks[0, :] = 0xFF
+            blocks[1, :] = 0x00
+            for off in synth._F16_FIELDS[tid]:
+                blocks[0, off:off + 2] = np.array([0x3C00], dtype=np.uint16).view(np.uint8)
+            raw = blocks.reshape(-1)
+            numel = n_blocks * be - 5
+            v = torch.from_numpy(quants.dequantize(raw, gtype).reshape(-1).astype(np.float32)[:numel].copy())
+            out = {"raw": raw, "numel": np.int64(numel), "f32": bits(v), "f16": bits(v.to(torch.float16)), "bf16": bits(v.to(torch.bfloat16)),
+                   "source": np.array(f"gguf-py {getattr(gguf, '__version__', '0.19.0')} quants.dequantize")}
+            for mid, fin in CAST2:
+                out[f"{mid}_then_{fin}"] = bits(v.to(TORCH[mid]).to(TORCH[fin]))
+            np.savez_compressed(os.path.join(HERE, f"decode_{name}_ggml.npz"), **out)
+            print(name, "via gguf-py", numel, "elements")
     except ImportError:
-        print("gguf-py not installed: ggml-order fixtures not regenerated")
+        print("gguf-py not installed: ggml-order and extra-format fixtures not regenerated")
 
     # --- a small file through the reference's parser and read_tensor ---------
     from pfhe_b200 import synth

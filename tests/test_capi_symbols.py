@@ -30,14 +30,16 @@ def test_version_and_nbytes():
     assert L.pfhe_tensor_nbytes(2, 32) == 18 and L.pfhe_tensor_nbytes(2, 33) == 36
     assert L.pfhe_tensor_nbytes(3, 64) == 40 and L.pfhe_tensor_nbytes(8, 1) == 34
     assert L.pfhe_tensor_nbytes(0, 5) == 20 and L.pfhe_tensor_nbytes(1, 5) == 10 and L.pfhe_tensor_nbytes(30, 5) == 10
-    assert L.pfhe_tensor_nbytes(6, 32) == _native.ERR_BAD_TYPE
+    assert L.pfhe_tensor_nbytes(6, 32) == 22 and L.pfhe_tensor_nbytes(7, 33) == 48          # Q5_0, Q5_1
+    assert [L.pfhe_tensor_nbytes(t, 257) for t in (10, 11, 12, 13, 14)] == [168, 220, 288, 352, 420]   # K-quants
+    assert L.pfhe_tensor_nbytes(9, 32) == _native.ERR_BAD_TYPE
     assert "not one of" in _native.last_error()
 
 
 def test_argument_errors_map_to_reference_exceptions():
     L = _native.lib()
     # all of these are rejected before any CUDA call
-    rc = L.pfhe_dequant_launch(12, 0, None, 0, None, 0, 32, None)
+    rc = L.pfhe_dequant_launch(15, 0, None, 0, None, 0, 32, None)
     with pytest.raises(NotImplementedError):
         _native.check(rc)
     rc = L.pfhe_dequant_launch(2, 7, None, 18, None, 128, 32, None)

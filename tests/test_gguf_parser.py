@@ -88,13 +88,13 @@ def test_unsupported_tensor_type(tmp_path):
     synth.write_gguf(p, [synth.TensorSpec("w", (64,), gl.GGML_TYPE_F32)], contents={"w": np.zeros(64, np.float32)})
     raw = bytearray(p.read_bytes())
     i = raw.index(b"w" + struct.pack("<I", 1))           # name, n_dims
-    struct.pack_into("<I", raw, i + 1 + 4 + 8, gl.GGML_TYPE_Q5_0)
+    struct.pack_into("<I", raw, i + 1 + 4 + 8, gl.GGML_TYPE_Q8_1)
     p.write_bytes(bytes(raw))
     with gl.GGUFReader(p) as r:
-        assert r.tensors["w"].dtype_name == "Q5_0"
-        with pytest.raises(ValueError, match="Unknown dtype 6"):
+        assert r.tensors["w"].dtype_name == "Q8_1"
+        with pytest.raises(ValueError, match="Unknown dtype 9"):
             r.tensors["w"].nbytes
-        with pytest.raises(ValueError, match="Unknown dtype 6"):
+        with pytest.raises(ValueError, match="Unknown dtype 9"):
             r.read_tensor("w")
     assert gl.GGUFTensorInfo("x", 1, (4,), 99, 0).dtype_name == "UNKNOWN(99)"
 
@@ -123,7 +123,9 @@ def test_api_surface_and_defaults():
     assert (p["device"].default, p["dtype"].default, p["strict"].default) == ("cuda", torch.float16, False)
     p = sig(gl.tensor_loading_context).parameters
     assert (p["device"].default, p["dtype"].default) == ("cpu", torch.float32)
-    assert gl.QUANT_INFO == {0: (1, 4), 1: (1, 2), 30: (1, 2), 2: (32, 18), 3: (32, 20), 8: (32, 34)}
+    assert {t: gl.QUANT_INFO[t] for t in gl.REFERENCE_TYPES} == {0: (1, 4), 1: (1, 2), 30: (1, 2), 2: (32, 18), 3: (32, 20), 8: (32, 34)}
+    assert {t: gl.QUANT_INFO[t] for t in (6, 7, 10, 11, 12, 13, 14)} == {6: (32, 22), 7: (32, 24), 10: (256, 84), 11: (256, 110),
+                                                                         12: (256, 144), 13: (256, 176), 14: (256, 210)}
     for name in pfhe_b200.__all__:
         assert hasattr(pfhe_b200, name)
 

@@ -316,3 +316,37 @@ def test_nibble_order_option(small_llama):
     assert_same_bits(to_bits(lin.weight.data), want_ggml, "f16")
     with pytest.raises(ValueError):
         gl.GGUFReader(path, nibble_order="other")
+
+
+def test_k_quant_file_through_the_api(tmp_path):
+    """A file with the type mix of a llama.cpp Q4_K_M export goes through read_tensor, streaming and
+    patch_context; rows shard on whole 256-element blocks; the no-alloc entry point decodes them too."""
+    path = tmp_path / "kq.gguf"
+    specs = [synth.TensorSpec("token_embd.weight", (96, 512), gl.GGML_TYPE_Q4_K), synth.TensorSpec("a.weight", (64, 1024), gl.GGML_TYPE_Q6_K),
+             synth.TensorSpec("b.weight", (40, 256), gl.GGML_TYPE_Q5_K), synth.TensorSpec("c.weight", (16, 768), gl.GGML_TYPE_Q2_K),
+             synth.TensorSpec("d.weight", (8, 512), gl.GGML_TYPE_Q3_K), synth.TensorSpec("e.weight", (50, 64), gl.GGML_TYPE_Q5_0),
+             synth.TensorSpec("f.weight", (50, 96), gl.GGML_TYPE_Q5_1), synth.TensorSpec("n.weight", (512,), gl.GGML_TYPE_F32)]
+    synth.write_gguf(path, specs, seed=77)
+    with gl.GGUFReader(path) as r:
+        for n, info in r.tensors.items():
+            assert info.nbytes == synth.packed_nbytes(info.dtype, info.numel)
+            for k, dt in DT.items():
+                assert_same_bits(to_bits(r.read_tensor(n, device="cuda", dtype=dt)), _oracle_tensor(r, n, k), k, f"{n}->{k}")
+        whole = r.read_tensor("a.weight", device="cuda", dtype=torch.float16)
+        parts = [r.read_tensor("a.weight", device="cuda", dtype=torch.float16, rows=(a, b)) for a, b in ((0, 7), (7, 64))]
+        assert torch.equal(torch.cat(parts).view(torch.int16), whole.view(torch.int16))
+        want = {n: _oracle_tensor(r, n, "f16") for n in r.tensors}
+    with pfhe_b200.streaming_dequant_context(path, batch_size=3, dtype=torch.float16) as s:
+        for batch in s.iter_batches():
+            for n, t in batch.items():
+                assert_same_bits(to_bits(t), want[n], "f16", n)
+    import ctypes
+    from pfhe_b200 import _native
+    with gl.GGUFReader(path) as r:
+        info = r.tensors["token_embd.weight"]
+        raw = np.frombuffer(r.read_tensor_raw("token_embd.weight"), dtype=np.uint8).copy()
+    dst = torch.zeros(info.numel, dtype=torch.float16, device="cuda")
+    _native.check(_native.lib().pfhe_dequant_from_host_noalloc(info.dtype, _native.OUT_F16, raw.ctypes.data, raw.size, dst.data_ptr(),
+                                                              info.numel * 2, info.numel, None))
+    torch.cuda.synchronize()
+    assert_same_bits(to_bits(dst), want["token_embd.weight"], "f16", "no-alloc Q4_K")

@@ -300,3 +300,61 @@ def test_ggml_order_in_a_batch():
     torch.cuda.synchronize()
     for (src, dst), want, case in zip(keep, wants, cases):
         assert_same_bits(to_bits(dst), want, "bf16", str(case))
+
+
+# --- formats beyond the reference's six (Q5_0, Q5_1, K-quants), oracle pinned to gguf-py -----------
+from conftest import EXTRA_FORMATS, load_golden_extra
+
+
+@pytest.mark.parametrize("fmt", list(EXTRA_FORMATS))
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+@pytest.mark.parametrize("variant", ["default", "staged_small_tiles", "per_element"])
+def test_extra_formats_golden(fmt, dtype, variant):
+    g = load_golden_extra(fmt)
+    cfg = VARIANTS[variant]
+    got = decode_on_gpu(EXTRA_FORMATS[fmt], g["raw"], int(g["numel"]), dtype, cfg=cfg)
+    assert_same_bits(to_bits(got), g[dtype], dtype, f"{fmt}->{dtype} [{variant}]")
+
+
+@pytest.mark.parametrize("fmt", list(EXTRA_FORMATS))
+@pytest.mark.parametrize("mid,fin", CAST2)
+def test_extra_formats_two_step_rounding(fmt, mid, fin):
+    g = load_golden_extra(fmt)
+    got = decode_on_gpu(EXTRA_FORMATS[fmt], g["raw"], int(g["numel"]), fin, mid=mid)
+    assert_same_bits(to_bits(got), g[f"{mid}_then_{fin}"], fin, f"{fmt}->{mid}->{fin}")
+
+
+@pytest.mark.parametrize("fmt", list(EXTRA_FORMATS))
+def test_extra_formats_sizes_offsets_and_all_scales(fmt):
+    t = EXTRA_FORMATS[fmt]
+    be, bb = synth.QUANT_INFO[t]
+    rng = np.random.default_rng(t)
+    # every finite fp16 pattern in every fp16 field, random payload
+    h = np.arange(1 << 16, dtype=np.uint32)
+    h = h[(h & 0x7C00) != 0x7C00].astype(np.uint16)
+    n_blocks = h.size // (8 if be == 256 else 1)
+    blocks = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+    for off in synth._F16_FIELDS[t]:
+        blocks[:, off:off + 2] = rng.permutation(h)[:n_blocks].view(np.uint8).reshape(-1, 2)
+    raw, numel = blocks.reshape(-1), n_blocks * be
+    for dtype in OUT_DTYPES:
+        want = c_oracle.read_tensor(t, raw, numel, dtype, n_threads=8)
+        assert_same_bits(to_bits(decode_on_gpu(t, raw, numel, dtype)), want, dtype, f"{fmt} all scales ->{dtype}")
+    # ragged sizes, sources off a 16-byte line (even and odd), destination off a 16-byte line
+    for numel in (1, 31, be - 1, be + 1, 8 * be - 3, 8 * be + 9, 100003):
+        raw = synth.random_packed(t, numel, np.random.default_rng(numel))
+        want = np_oracle.read_tensor(t, raw, numel, "bf16")
+        for skew, dskew in ((0, 0), (6, 0), (3, 0), (0, 1)):
+            got = decode_on_gpu(t, raw, numel, "bf16", skew=skew, dst_skew_elems=dskew)
+            assert_same_bits(to_bits(got), want, "bf16", f"{fmt} n={numel} skew={skew} dst+{dskew}")
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q6_K", "Q5_0"])
+def test_extra_formats_large(fmt):
+    t = EXTRA_FORMATS[fmt]
+    numel = 8192 * 4096 + 256 * 3
+    raw = synth.random_packed(t, numel, np.random.default_rng(50))
+    want = c_oracle.read_tensor(t, raw, numel, "f16", n_threads=8)
+    assert_same_bits(to_bits(decode_on_gpu(t, raw, numel, "f16")), want, "f16", fmt)
+    with pytest.raises(ValueError):
+        decode_on_gpu(t, raw, numel, "f16", cfg={"variant": 5, "tile_blocks": 64, "stages": 2, "threads": 256, "ctas_per_sm": 2})

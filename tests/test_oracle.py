@@ -64,9 +64,9 @@ def test_short_source_raises_value_error():
 
 def test_unknown_type():
     with pytest.raises(ValueError):
-        np_oracle.nbytes(12, 256)
+        np_oracle.nbytes(15, 256)
     with pytest.raises(NotImplementedError):
-        c_oracle.read_tensor(12, np.zeros(256, dtype=np.uint8), 32)
+        c_oracle.read_tensor(15, np.zeros(512, dtype=np.uint8), 32)
 
 
 @pytest.mark.parametrize("fmt", list(FORMATS))
@@ -107,3 +107,21 @@ def test_ggml_nibble_order_matches_gguf_py(fmt, dtype):
     assert np.array_equal(alt[:, 16:].view(np.uint32), ref[:, 1::2].view(np.uint32))
     with pytest.raises(NotImplementedError):
         np_oracle.decode_f32(FORMATS["Q8_0"] | np_oracle.GGML_ORDER, g["raw"], 32)
+
+
+@pytest.mark.parametrize("fmt", ["Q5_0", "Q5_1", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K"])
+@pytest.mark.parametrize("dtype", OUT_DTYPES)
+def test_extra_formats_match_gguf_py(fmt, dtype):
+    """Formats the reference cannot decode: both oracles against vectors made by gguf-py."""
+    from conftest import CAST2, EXTRA_FORMATS, load_golden_extra
+    g = load_golden_extra(fmt)
+    t = EXTRA_FORMATS[fmt]
+    n = int(g["numel"])
+    assert_same_bits(np_oracle.read_tensor(t, g["raw"], n, dtype), g[dtype], dtype, fmt)
+    assert_same_bits(c_oracle.read_tensor(t, g["raw"], n, dtype, n_threads=3), g[dtype], dtype, fmt)
+    if dtype == "f32":
+        for mid, fin in CAST2:
+            assert_same_bits(c_oracle.read_tensor(t, g["raw"], n, fin, via_dtype=mid), g[f"{mid}_then_{fin}"], fin, fmt)
+        assert np_oracle.nbytes(t, n) == g["raw"].size
+        with pytest.raises(ValueError, match="Data too short"):
+            np_oracle.read_tensor(t, g["raw"][:-1], n, "f32")

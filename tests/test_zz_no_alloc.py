@@ -87,7 +87,7 @@ def test_largest_accepted_and_first_rejected_size():
 def test_argument_errors():
     dst = torch.zeros(64, dtype=torch.float16, device="cuda")
     raw = np.zeros(36, dtype=np.uint8)
-    assert _no_alloc_entry_point(12, raw, 32, dst) == _native.ERR_BAD_TYPE
+    assert _no_alloc_entry_point(15, raw, 32, dst) == _native.ERR_BAD_TYPE
     assert _no_alloc_entry_point(2, raw[:17], 32, dst) == _native.ERR_SHORT_SOURCE
     L = _native.lib()
     assert L.pfhe_dequant_from_host_noalloc(2, 1, raw.ctypes.data, 36, dst.data_ptr(), 10, 32, None) == _native.ERR_SHORT_DEST
