@@ -637,6 +637,8 @@ def run_sweep(args) -> None:
     L = _native.lib()
     peak, _ = measured_peaks()
     fmts = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8, "F16": 1, "BF16": 30, "F32": 0}
+    if args.sweep_extra_formats:   # the formats beyond the reference's six
+        fmts = {"Q5_0": 6, "Q5_1": 7, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
     outs = {"f16": (_native.OUT_F16, torch.float16), "bf16": (_native.OUT_BF16, torch.bfloat16)}
     sizes = [64 << 10, 1 << 20, 16 << 20, 64 << 20, 256 << 20, 1 << 30, 2 << 30]
     row_lens = [4096, 8192, 14336]
@@ -648,7 +650,7 @@ def run_sweep(args) -> None:
         for si, target in enumerate(sizes):
             if target > args.sweep_max_bytes:
                 continue
-            K = row_lens[si % len(row_lens)]
+            K = row_lens[si % len(row_lens)] if fname not in ("Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K") else (4096, 8192, 14336)[si % 3]
             row_bytes = L.pfhe_tensor_nbytes(t, K)
             rows = max(1, target // row_bytes)
             numel = rows * K
@@ -702,6 +704,7 @@ def main() -> None:
                     help="FORMAT:OUT:NUMEL[:LAUNCHES] -- run only a few launches of one kernel (for profilers)")
     ap.add_argument("--sweep", action="store_true", help="kernel-roofline sweep over sizes, formats and dtypes")
     ap.add_argument("--sweep-max-bytes", type=int, default=2 << 30)
+    ap.add_argument("--sweep-extra-formats", action="store_true", help="sweep Q5_0, Q5_1 and the K-quants instead")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)

@@ -399,6 +399,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     if (tiles_per_cta < a.stages) a.stages = (int)tiles_per_cta;
 
     size_t smem = (size_t)a.stages * (a.tile_blocks * bb + 16);
+    if (ggml_type == T_Q4_K || ggml_type == T_Q5_K) smem += (size_t)a.tile_blocks * 8 * sizeof(float2);
     StagedFn fn = k.staged[ss];
     if (variant == 3) {
         smem = ((smem + 127) & ~(size_t)127) + 2 * (size_t)a.tile_blocks * be * osz;

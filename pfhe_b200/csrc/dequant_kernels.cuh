@@ -446,12 +446,14 @@ struct StageRing {
     int stages;
     int stage_bytes;
     uint32_t parity_bits;
+    float2 *scale_table;   // per-tile (multiplier, offset) table for the formats that use one, behind the stages
 };
 
 // Decodes one staged tile: blocks [tb0, tb0 + nb) of `pt`, whose packed bytes
 // start at `tile` in shared memory.  Called by every thread of the CTA.
 template <int T, int MID, int OUT, bool kStream>
-__device__ __forceinline__ void decode_tile(const PackedTensor &pt, int64_t tb0, int nb, const uint8_t *tile)
+__device__ __forceinline__ void decode_tile(const PackedTensor &pt, int64_t tb0, int nb, const uint8_t *tile,
+                                            float2 *scale_table = nullptr)
 {
     constexpr int BB = Fmt<T>::kBytes;
     constexpr int VEC = 16 / OutT<OUT>::kSize;       // outputs per 16-byte store
@@ -470,10 +472,30 @@ __device__ __forceinline__ void decode_tile(const PackedTensor &pt, int64_t tb0,
     uint8_t *op = out + (size_t)threadIdx.x * 16;
     const int bstep = (blockDim.x / UPB) * BB;
     const int ostep = blockDim.x * 16;
+    if constexpr (ScaleTable<T>::kGroups > 0) {
+        // Pass 1: every group's multiplier and offset once, into shared memory.
+        constexpr int G = ScaleTable<T>::kGroups;
+        constexpr int GE = Fmt<T>::kElems / G;                     // elements per group (a multiple of VEC)
+        for (int g = threadIdx.x; g < nb * G; g += blockDim.x) {
+            float dl, ml;
+            extra_scales<T>(tile + (g / G) * BB, (g % G) * GE, &dl, &ml);
+            scale_table[g] = make_float2(dl, ml);
+        }
+        __syncthreads();
+        const float2 *sp = scale_table + (threadIdx.x / UPB) * G + (c * VEC) / GE;
+        const int sstep = (blockDim.x / UPB) * G;
 #pragma unroll 4
-    for (int u = threadIdx.x; u < full_units; u += blockDim.x, bp += bstep, op += ostep) {
-        const uint4 r = decode_unit<T, MID, OUT, true>(bp, c);
-        store16<kStream>(op, r);
+        for (int u = threadIdx.x; u < full_units; u += blockDim.x, bp += bstep, op += ostep, sp += sstep) {
+            const float2 sc = *sp;
+            const uint4 r = extra_unit_scaled<T, MID, OUT>(bp, c, sc.x, sc.y);
+            store16<kStream>(op, r);
+        }
+    } else {
+#pragma unroll 4
+        for (int u = threadIdx.x; u < full_units; u += blockDim.x, bp += bstep, op += ostep) {
+            const uint4 r = decode_unit<T, MID, OUT, true>(bp, c);
+            store16<kStream>(op, r);
+        }
     }
     // Ragged end of the tensor (n_elements not a multiple of VEC): scalar stores.
     if (valid % VEC != 0 && threadIdx.x == 0) {
@@ -524,7 +546,7 @@ __device__ __forceinline__ bool decode_run(const PackedTensor &pt, int64_t first
 
         const int64_t tb0 = first + (int64_t)k * stride;
         const int nb = (int)((end - tb0) < tile_blocks ? (end - tb0) : tile_blocks);
-        decode_tile<T, MID, OUT, kStream>(pt, tb0, nb, ring.smem + (size_t)s * ring.stage_bytes + pt.skew);
+        decode_tile<T, MID, OUT, kStream>(pt, tb0, nb, ring.smem + (size_t)s * ring.stage_bytes + pt.skew, ring.scale_table);
         __syncthreads();                                           // all reads of stage s done
         if (threadIdx.x == 0 && k + ring.stages < n_tiles) issue(k + ring.stages);
     }
@@ -550,6 +572,7 @@ __device__ __forceinline__ void ring_init(StageRing &ring, uint8_t *smem, uint64
     ring.stages = stages;
     ring.stage_bytes = stage_bytes;
     ring.parity_bits = 0;
+    ring.scale_table = reinterpret_cast<float2 *>(smem + (size_t)stages * stage_bytes);   // 16-byte aligned
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

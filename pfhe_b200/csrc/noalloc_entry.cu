@@ -75,7 +75,8 @@ void launch_blocks(const uint8_t *src, void *dst, int64_t n, int *status, int sm
     const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
     const int target = (OUT == O_F32 ? 8192 : 16384) / Fmt<T>::kElems;   // 34.8 KB of shared memory at most: no opt-in needed
     a.tile_blocks = groups_per_cta * 8 < target ? (int)(groups_per_cta * 8) : target;
-    const size_t smem = (size_t)a.stages * (a.tile_blocks * Fmt<T>::kBytes + 16);
+    const size_t smem = (size_t)a.stages * (a.tile_blocks * Fmt<T>::kBytes + 16) +
+                        (size_t)a.tile_blocks * ScaleTable<T>::kGroups * sizeof(float2);
     dequant_blocks_staged<T, OUT, OUT, true><<<(unsigned)grid, 256, smem, stream>>>(a);
 }
 
