@@ -208,6 +208,17 @@ int pfhe_dequant_from_host_noalloc(int ggml_type, int out_dtype,
  */
 int pfhe_device_status(int device);
 
+/*
+ * Self-test of the failure path (no counterpart in the reference): launches a
+ * one-warp kernel that waits, with the same bounded wait the decode kernels
+ * use, on a barrier that nothing completes.  After limit_ms (1..1000) the
+ * kernel gives up, records the failure in the device status word and returns;
+ * the call synchronises `stream` and stores the time the kernel waited.  The
+ * next pfhe_device_status() then reports PFHE_ERR_DEVICE_WAIT.  Nothing
+ * faults, traps or hangs.
+ */
+int pfhe_selftest_bounded_wait(int limit_ms, int64_t *waited_ns, void *stream);
+
 /* Number of kernels this library has launched in this process (all threads). */
 int64_t pfhe_launch_count(void);
 

@@ -571,6 +571,29 @@ int pfhe_dequant_launch_batch_ex(const pfhe_tensor_desc *tensors, int n_tensors,
     return launch_batch(tensors, n_tensors, static_cast<cudaStream_t>(stream), cfg);
 }
 
+int pfhe_selftest_bounded_wait(int limit_ms, int64_t *waited_ns, void *stream_)
+{
+    if (limit_ms < 1 || limit_ms > 1000) { set_error("limit_ms must be 1..1000"); return PFHE_ERR_BAD_ARG; }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int dev = 0, rc;
+    if ((rc = current_device(&dev))) return rc;
+    int *status = nullptr;
+    if ((rc = status_word(dev, &status))) return rc;
+    unsigned long long *d_waited = nullptr;
+    cudaError_t e = cudaMalloc(&d_waited, sizeof *d_waited);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(selftest)");
+    bounded_wait_selftest<<<1, 32, 0, stream>>>((uint64_t)limit_ms * 1000000ull, status, d_waited);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    unsigned long long waited = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&waited, d_waited, sizeof waited, cudaMemcpyDeviceToHost);
+    cudaFree(d_waited);
+    if (e != cudaSuccess) return cuda_fail(e, "bounded-wait self-test");
+    if (waited_ns) *waited_ns = (int64_t)waited;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return PFHE_OK;
+}
+
 int pfhe_device_status(int device)
 {
     int dev = device;

@@ -606,6 +606,28 @@ __global__ void __launch_bounds__(512) dequant_blocks_staged(const BlockKernelAr
 }
 
 // ---------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp waits on a barrier that nothing will
+// ever complete, for at most limit_ns, then reports through the status word
+// exactly as the decode kernels do.  No fault, no trap, no endless loop: the
+// kernel always returns.
+// ---------------------------------------------------------------------------
+static __global__ void bounded_wait_selftest(uint64_t limit_ns, int *status, unsigned long long *waited_ns)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint64_t t0 = global_timer_ns();
+        const bool ok = mbar_wait_bounded(&bar, 0, limit_ns);
+        *waited_ns = global_timer_ns() - t0;
+        if (!ok) atomicExch(status, DEV_WAIT_TIMEOUT);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Variant 5: every warp runs its own ring of stages; after set-up there is no
 // CTA-wide barrier.  Tiles (of `tile_blocks` blocks, per warp) are dealt
 // round-robin to all warps of the grid, so the warps of a CTA work on adjacent

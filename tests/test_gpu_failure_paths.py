@@ -1,0 +1,69 @@
+"""Failure detection without faulting anything: bounded waits on the device and on the host."""
+import ctypes
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from pfhe_b200 import _native, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_wait_runs_out_and_is_reported():
+    """A kernel waits on a barrier nothing completes; after the limit it records the failure and
+    returns, the host reads PFHE_ERR_DEVICE_WAIT once, and the device keeps working."""
+    L = _native.lib()
+    assert L.pfhe_device_status(-1) == _native.OK                       # clean slate
+    waited = ctypes.c_int64(0)
+    t0 = time.perf_counter()
+    _native.check(L.pfhe_selftest_bounded_wait(50, ctypes.byref(waited), None))
+    wall = time.perf_counter() - t0
+    assert 45e6 <= waited.value <= 400e6, waited.value                  # gave up after about the limit
+    assert wall < 5.0
+    rc = L.pfhe_device_status(-1)
+    assert rc == _native.ERR_DEVICE_WAIT
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        _native.check(rc)
+    assert L.pfhe_device_status(-1) == _native.OK                       # reading clears it
+    # the context is intact: a normal decode still runs and is correct
+    raw = synth.random_packed(2, 32 * 1000, np.random.default_rng(1))
+    src = torch.from_numpy(raw).cuda()
+    dst = torch.empty(32 * 1000, dtype=torch.float16, device="cuda")
+    _native.check(L.pfhe_dequant_launch(2, 1, src.data_ptr(), src.numel(), dst.data_ptr(), dst.numel() * 2, 32 * 1000, None))
+    torch.cuda.synchronize()
+    assert L.pfhe_device_status(-1) == _native.OK
+    assert L.pfhe_selftest_bounded_wait(0, None, None) == _native.ERR_BAD_ARG
+    assert L.pfhe_selftest_bounded_wait(5000, None, None) == _native.ERR_BAD_ARG
+
+
+def test_host_wait_deadline():
+    """pfhe_loader_wait returns PFHE_ERR_TIMEOUT instead of blocking when work is still queued,
+    and PFHE_OK once it has drained."""
+    L = _native.lib()
+    handle = ctypes.c_void_p()
+    _native.check(L.pfhe_loader_create(torch.cuda.current_device(), 2, 32 << 20, 2, ctypes.byref(handle)))
+    try:
+        numel = 32 * 4_000_000                                          # 72 MB packed, three chunks
+        raw = synth.random_packed(2, numel, np.random.default_rng(2))
+        dst = torch.empty(numel, dtype=torch.float16, device="cuda")
+        gate = torch.cuda.Event()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            torch.cuda._sleep(int(2e8))                                  # ~0.1 s of queued work ahead of the decodes
+            _native.check(L.pfhe_loader_submit(handle, raw.ctypes.data, raw.size, 2, 1, 1, dst.data_ptr(), numel * 2, numel,
+                                               stream.cuda_stream))
+        rc = L.pfhe_loader_wait(handle, 0)
+        assert rc in (_native.ERR_TIMEOUT, _native.OK)
+        if rc == _native.ERR_TIMEOUT:
+            assert "not finished" in _native.last_error()
+            with pytest.raises(TimeoutError):
+                _native.check(rc)
+        _native.check(L.pfhe_loader_wait(handle, 60000))
+        stream.synchronize()
+        from oracle import np_oracle
+        want = np_oracle.read_tensor(2, raw[: 18 * 1000], 32 * 1000, "f16")
+        assert np.array_equal(dst[: 32 * 1000].cpu().view(torch.int16).numpy().view(np.uint16), want.view(np.uint16))
+    finally:
+        assert L.pfhe_loader_destroy(handle) == 0
