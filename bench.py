@@ -174,11 +174,12 @@ def run_reference_arm(args) -> None:
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32 arithmetic, f16 out", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": sample,
                    "note": "the reference is pure Python and is not installed on this machine; this is the "
                            "oracle's per-block loop port of gguf_loader.py:430-476, which keeps its cost structure"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample,
+                         "also": cpu_extras(synth.random_packed(Q4_0, NUMEL, np.random.default_rng(2)))},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -327,9 +328,11 @@ def run_gpu_arm(args) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": total_ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 multiply of exact small integers (bit-identical to the reference's f32 path), f16 out",
+            "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "tensors_per_step": batch, "parallelism": f"independent tensors per GPU x{world}",
+                       "arithmetic": "one fp16 multiply of the exactly represented (q-8) by d per element: bit-identical to "
+                                     "the reference's fp32 product rounded to fp16",
                        "l2": f"inputs larger than L2: {batch} distinct tensors, {batch * algo_bytes / 1e6:.0f} MB touched per step",
                        "in_bytes_per_tensor": in_bytes, "out_bytes_per_tensor": out_bytes},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

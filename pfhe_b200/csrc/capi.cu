@@ -112,11 +112,18 @@ struct ElemKernels {
 
 template <int T, int MID, int OUT> static BlockKernels block_kernels()
 {
-    return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
-                        dequant_blocks_staged_out<T, MID, OUT>,
-                        {dequant_blocks_warp_rings<T, MID, OUT, false>, dequant_blocks_warp_rings<T, MID, OUT, true>},
-                        {dequant_blocks_direct<T, MID, OUT, false>, dequant_blocks_direct<T, MID, OUT, true>},
-                        dequant_any_alignment<T, MID, OUT>};
+    if constexpr (MID == OUT) {
+        return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
+                            dequant_blocks_staged_out<T, MID, OUT>,
+                            {dequant_blocks_warp_rings<T, MID, OUT, false>, dequant_blocks_warp_rings<T, MID, OUT, true>},
+                            {dequant_blocks_direct<T, MID, OUT, false>, dequant_blocks_direct<T, MID, OUT, true>},
+                            dequant_any_alignment<T, MID, OUT>};
+    } else {
+        // two-step roundings only need the main kernel and the fallback; the measured
+        // alternatives (variants 2, 3, 5) are built for the plain case alone
+        return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
+                            nullptr, {nullptr, nullptr}, {nullptr, nullptr}, dequant_any_alignment<T, MID, OUT>};
+    }
 }
 template <int T, int MID, int OUT> static ElemKernels elem_kernels()
 {
