@@ -350,3 +350,46 @@ def test_k_quant_file_through_the_api(tmp_path):
                                                               info.numel * 2, info.numel, None))
     torch.cuda.synchronize()
     assert_same_bits(to_bits(dst), want["token_embd.weight"], "f16", "no-alloc Q4_K")
+
+
+def test_config3_llama2_7b_file_streamed_at_full_size():
+    """The 7B-shaped benchmark file at full size (291 tensors, 3.9 GB packed, 13.5 GB of fp16) through
+    streaming_dequant_context(batch_size=8).  The file is written as a seeded 4Mi-element tile per
+    tensor repeated to length, so every tensor must decode to the oracle's decode of its tile,
+    repeated -- a size-independent check of all 6.7 G elements."""
+    from oracle import c_oracle
+    base = "/dev/shm" if os.access("/dev/shm", os.W_OK) else None
+    if base is None or os.statvfs(base).f_bavail * os.statvfs(base).f_frsize < 6e9:
+        pytest.skip("needs 6 GB in /dev/shm")
+    path = os.path.join(base, f"pfhe_test_7b_{os.getpid()}.gguf")
+    specs = synth.llama_specs(synth.LLAMA2_7B)
+    tile_elems = 1 << 22
+    try:
+        size = synth.write_gguf_tiled(path, specs, synth.llama_metadata(synth.LLAMA2_7B), seed=33, threads=8, tile_elems=tile_elems)
+        assert abs(size - 3.92e9) < 0.02e9 and len(specs) == 291
+        expected = {}
+        seen = 0
+        with pfhe_b200.streaming_dequant_context(path, batch_size=8, device="cuda", dtype=torch.float16) as stream:
+            assert stream.tensor_names == [s.name for s in specs]
+            for batch in stream.iter_batches():
+                assert len(batch) <= 8
+                for name, t in batch.items():
+                    i = stream.tensor_names.index(name)
+                    sp = specs[i]
+                    assert tuple(t.shape) == sp.shape and t.dtype == torch.float16
+                    n_tile = min(tile_elems, -(-sp.numel // 32) * 32) if sp.ggml_type != gl.GGML_TYPE_F32 else min(tile_elems, sp.numel)
+                    tile_raw = synth.random_packed(sp.ggml_type, n_tile, np.random.default_rng([33, i]))
+                    want = torch.from_numpy(c_oracle.read_tensor(sp.ggml_type, tile_raw, n_tile, "f16", n_threads=8).view(np.int16)).cuda()
+                    flat = t.reshape(-1).view(torch.int16)
+                    whole = flat.numel() // n_tile
+                    if whole:
+                        assert bool((flat[: whole * n_tile].view(whole, n_tile) == want.unsqueeze(0)).all()), name
+                    rest = flat.numel() - whole * n_tile
+                    if rest:
+                        assert torch.equal(flat[whole * n_tile:], want[:rest]), name
+                    seen += 1
+                del batch
+        assert seen == 291
+    finally:
+        if os.path.exists(path):
+            os.unlink(path)
