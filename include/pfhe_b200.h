@@ -209,6 +209,23 @@ int pfhe_dequant_from_host_noalloc(int ggml_type, int out_dtype,
 int pfhe_device_status(int device);
 
 /*
+ * Decode-time product on packed weights: y[m][n] = sum_k x[m][k] * W[n][k] for
+ * batch m = 1..8, W of shape (rows, cols) kept in its GGUF block format (Q4_0,
+ * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER) and decoded on the
+ * fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
+ * (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight
+ * to fp16 in device memory and then call F.linear.  Every weight takes exactly
+ * the fp16 value pfhe_dequant_launch(..., PFHE_OUT_F16) gives it, x is fp16,
+ * products and sums are fp32; the result differs from an fp32 reference only by
+ * summation order.  cols must be a multiple of 256; w_dev and x_dev 16-byte
+ * aligned; x is [batch][ldx] halves, y is [batch][ldy] of y_dtype (PFHE_OUT_F32
+ * or PFHE_OUT_F16).
+ */
+int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_bytes, int64_t rows, int64_t cols,
+                        const void *x_dev, int batch, int64_t ldx,
+                        void *y_dev, int y_dtype, int64_t ldy, void *stream);
+
+/*
  * Self-test of the failure path (no counterpart in the reference): launches a
  * one-warp kernel that waits, with the same bounded wait the decode kernels
  * use, on a barrier that nothing completes.  After limit_ms (1..1000) the

@@ -1,0 +1,132 @@
+"""Weights that stay in their GGUF block format on the GPU.
+
+Mirrors ``QuantizedTensor``, ``quantized_matmul_q4_0`` / ``quantized_matmul_q8_0`` and
+``QuantizedLinear`` of the reference (src/phfe/inference/gguf_cuda.py:247-401).  The reference
+dequantises the whole weight to fp16 on every call and then runs ``F.linear``; here a small batch
+(up to 8 rows of activations, the decode phase of generation) goes through
+``pfhe_quantized_gemv``, which reads the packed bytes once and never writes the fp16 weight.
+Larger batches decode the weight with the block-decode kernel and call ``F.linear``, as the
+reference does.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native
+from .gguf_loader import GGML_TYPE_F16, GGML_TYPE_F32, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0, QUANT_INFO
+from .resident import decode_resident
+
+GEMV_TYPES = (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0)
+GEMV_MAX_BATCH = 8
+
+
+class QuantizedTensor:
+    """Packed GGUF blocks on the GPU plus their logical shape (reference gguf_cuda.py:247-296)."""
+
+    def __init__(self, raw_data: torch.Tensor, shape: Tuple[int, ...], quant_type: int, device: str = "cuda",
+                 nibble_order: str = "reference"):
+        if quant_type not in QUANT_INFO:
+            raise ValueError(f"Unsupported quant type: {quant_type}")
+        self.raw_data = raw_data.to(device).contiguous().view(torch.uint8)
+        self.shape = tuple(shape)
+        self.quant_type = quant_type
+        self.device = device
+        self.nibble_order = nibble_order
+        self.numel = 1
+        for d in self.shape:
+            self.numel *= d
+
+    @property
+    def kernel_type(self) -> int:
+        if self.nibble_order == "ggml" and self.quant_type in (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1):
+            return self.quant_type | _native.TYPE_FLAG_GGML_ORDER
+        return self.quant_type
+
+    def dequantize(self, dtype: torch.dtype = torch.float16) -> torch.Tensor:
+        """Full decode (fp16 by default, as in the reference)."""
+        return decode_resident([(self.raw_data, self.kernel_type, self.shape)], dtype)[0]
+
+    @property
+    def nbytes(self) -> int:
+        return self.raw_data.numel()
+
+    @property
+    def compression_ratio(self) -> float:
+        return self.numel * 2 / self.nbytes
+
+
+def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int, int], quant_type: int,
+                     nibble_order: str = "reference") -> torch.Tensor:
+    """``x @ W.T`` for packed ``W`` of logical shape ``(out_features, in_features)``; returns fp16.
+
+    ``x`` is ``[..., in_features]``.  At most 8 rows of activations, an in_features that is a multiple of
+    256 and a Q4_0 / Q4_1 / Q8_0 weight take the fused kernel; everything else decodes then multiplies.
+    """
+    out_features, in_features = w_shape
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, in_features).to(torch.float16)
+    batch = x2.shape[0]
+    ktype = quant_type
+    if nibble_order == "ggml" and quant_type in (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1):
+        ktype |= _native.TYPE_FLAG_GGML_ORDER
+    fused = (quant_type in GEMV_TYPES and 1 <= batch <= GEMV_MAX_BATCH and in_features % 256 == 0
+             and x2.is_cuda and w_quant.is_cuda and w_quant.data_ptr() % 16 == 0)
+    if not fused:
+        w = decode_resident([(w_quant.contiguous().view(torch.uint8), ktype, (out_features, in_features))], torch.float16)[0]
+        return torch.nn.functional.linear(x2, w).reshape(*lead, out_features)
+    x2 = x2.contiguous()
+    if x2.data_ptr() % 16:
+        x2 = x2.clone()
+    y = torch.empty((batch, out_features), dtype=torch.float16, device=x2.device)
+    with torch.cuda.device(x2.device):
+        _native.check(_native.lib().pfhe_quantized_gemv(
+            ktype, w_quant.data_ptr(), w_quant.numel() * w_quant.element_size(), out_features, in_features,
+            x2.data_ptr(), batch, in_features, y.data_ptr(), _native.OUT_F16, out_features,
+            torch.cuda.current_stream(x2.device).cuda_stream))
+    return y.reshape(*lead, out_features)
+
+
+def quantized_matmul_q8_0(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int, int]) -> torch.Tensor:
+    """Reference gguf_cuda.py:299-330."""
+    return quantized_matmul(x, w_quant, w_shape, GGML_TYPE_Q8_0)
+
+
+def quantized_matmul_q4_0(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int, int]) -> torch.Tensor:
+    """Reference gguf_cuda.py:333-351."""
+    return quantized_matmul(x, w_quant, w_shape, GGML_TYPE_Q4_0)
+
+
+class QuantizedLinear(torch.nn.Module):
+    """Linear layer whose weight stays packed on the GPU (reference gguf_cuda.py:354-401)."""
+
+    def __init__(self, in_features: int, out_features: int, quant_type: int, raw_weight: torch.Tensor,
+                 bias: Optional[torch.Tensor] = None, nibble_order: str = "reference"):
+        super().__init__()
+        if quant_type not in QUANT_INFO or quant_type in (GGML_TYPE_F16, GGML_TYPE_F32):
+            raise ValueError(f"Unsupported quant type: {quant_type}")
+        self.in_features = in_features
+        self.out_features = out_features
+        self.quant_type = quant_type
+        self.nibble_order = nibble_order
+        self.register_buffer("weight_quant", raw_weight)
+        if bias is not None:
+            self.register_buffer("bias", bias)
+        else:
+            self.bias = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        out = quantized_matmul(x, self.weight_quant, (self.out_features, self.in_features), self.quant_type,
+                               self.nibble_order)
+        if self.bias is not None:
+            out = out + self.bias
+        return out
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.weight_quant.numel()
+
+    @property
+    def equivalent_fp16_bytes(self) -> int:
+        return self.in_features * self.out_features * 2

@@ -32,7 +32,7 @@ def decode_resident(items: Sequence[Tuple[torch.Tensor, int, Tuple[int, ...]]], 
     for i, (raw, ggml_type, shape) in enumerate(items):
         if raw.device != device or raw.dtype != torch.uint8 or not raw.is_contiguous():
             raise ValueError("packed tensors must be contiguous uint8 tensors on one CUDA device")
-        if ggml_type not in QUANT_INFO:
+        if (ggml_type & ~_native.TYPE_FLAG_GGML_ORDER) not in QUANT_INFO:
             raise NotImplementedError(f"Dequantization not implemented for type {ggml_type}")
         numel = 1
         for s in shape:

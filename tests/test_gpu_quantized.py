@@ -1,0 +1,101 @@
+"""Keep-quantised residency: the fused decode-and-multiply kernel against an fp32 torch reference.
+
+Floating-point kernel: weights are bit-exact (checked elsewhere), products are exact in fp32, only the
+order of the fp32 additions differs, so the tolerance is a few ulps of the sum of |terms|:
+|y - y_ref| <= 2e-5 * (|x| @ |W|.T) + one fp16 rounding of the result when the output is fp16."""
+import numpy as np
+import pytest
+import torch
+
+from pfhe_b200 import _native, synth
+from pfhe_b200.quantized import QuantizedLinear, QuantizedTensor, quantized_matmul, quantized_matmul_q4_0, quantized_matmul_q8_0
+from pfhe_b200.resident import decode_resident
+
+pytestmark = pytest.mark.gpu
+
+TYPES = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8}
+
+
+def _case(fmt, rows, cols, batch, seed):
+    t = TYPES[fmt]
+    raw = torch.from_numpy(synth.random_packed(t, rows * cols, np.random.default_rng(seed))).cuda()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(batch, cols, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+    return t, raw, x
+
+
+def _reference(t, raw, rows, cols, x):
+    w = decode_resident([(raw, t, (rows, cols))], torch.float16)[0].float()
+    xf = x.float()
+    return xf @ w.T, xf.abs() @ w.abs().T
+
+
+@pytest.mark.parametrize("fmt", list(TYPES))
+@pytest.mark.parametrize("rows,cols", [(16, 256), (4096, 4096), (1000, 1024), (11008, 4096), (33, 8192), (4096, 11008 // 256 * 256)])
+@pytest.mark.parametrize("batch", [1, 3, 8])
+def test_fused_gemv_matches_fp32_reference(fmt, rows, cols, batch):
+    t, raw, x = _case(fmt, rows, cols, batch, rows + cols + batch)
+    ref, bound = _reference(t, raw, rows, cols, x)
+    L = _native.lib()
+    y32 = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    _native.check(L.pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y32.data_ptr(),
+                                        _native.OUT_F32, rows, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    assert bool(((y32 - ref).abs() <= 2e-5 * bound + 1e-30).all()), float(((y32 - ref).abs() / (bound + 1e-30)).max())
+    y16 = quantized_matmul(x, raw, (rows, cols), t)
+    assert y16.dtype == torch.float16 and tuple(y16.shape) == (batch, rows)
+    assert bool(((y16.float() - ref).abs() <= 2e-5 * bound + ref.abs() * 2 ** -10 + 1e-7).all())
+
+
+def test_ggml_order_weights_and_wrappers():
+    rows, cols = 512, 2048
+    t, raw, x = _case("Q4_1", rows, cols, 2, 5)
+    tg = t | _native.TYPE_FLAG_GGML_ORDER
+    ref, bound = _reference(tg, raw, rows, cols, x)
+    y = quantized_matmul(x, raw, (rows, cols), t, nibble_order="ggml").float()
+    assert bool(((y - ref).abs() <= 2e-5 * bound + ref.abs() * 2 ** -10 + 1e-7).all())
+    # the reference-named wrappers and the module, with leading batch dimensions and a bias
+    t8, raw8, x8 = _case("Q8_0", rows, cols, 6, 6)
+    ref8, bound8 = _reference(t8, raw8, rows, cols, x8)
+    y8 = quantized_matmul_q8_0(x8.view(2, 3, cols), raw8, (rows, cols))
+    assert tuple(y8.shape) == (2, 3, rows)
+    assert bool(((y8.reshape(6, rows).float() - ref8).abs() <= 2e-5 * bound8 + ref8.abs() * 2 ** -10 + 1e-7).all())
+    t4, raw4, x4 = _case("Q4_0", rows, cols, 1, 7)
+    ref4, bound4 = _reference(t4, raw4, rows, cols, x4)
+    bias = torch.randn(rows, device="cuda", dtype=torch.float16)
+    lin = QuantizedLinear(cols, rows, t4, raw4, bias=bias)
+    out = lin(x4)
+    assert lin.weight_bytes == raw4.numel() and lin.equivalent_fp16_bytes == rows * cols * 2
+    assert bool(((out.float() - (ref4 + bias.float())).abs() <= 2e-5 * bound4 + (ref4.abs() + bias.abs().float()) * 2 ** -9 + 1e-6).all())
+    assert torch.equal(quantized_matmul_q4_0(x4, raw4, (rows, cols)), quantized_matmul(x4, raw4, (rows, cols), t4))
+    qt = QuantizedTensor(raw4, (rows, cols), t4)
+    assert qt.nbytes == raw4.numel() and abs(qt.compression_ratio - 32 * 2 / 18) < 1e-9
+    assert torch.equal(qt.dequantize(), decode_resident([(raw4, t4, (rows, cols))], torch.float16)[0])
+
+
+def test_large_batch_and_odd_shapes_fall_back_to_decode_then_linear():
+    rows, cols = 300, 96 * 32            # cols not a multiple of 256
+    t, raw, x = _case("Q4_0", rows, cols, 4, 8)
+    ref, bound = _reference(t, raw, rows, cols, x)
+    y = quantized_matmul(x, raw, (rows, cols), t)
+    assert bool(((y.float() - ref).abs() <= 1e-3 * bound + 1e-3).all())
+    t, raw, x = _case("Q8_0", 256, 1024, 20, 9)          # batch > 8
+    ref, bound = _reference(t, raw, 256, 1024, x)
+    y = quantized_matmul(x, raw, (256, 1024), t)
+    assert tuple(y.shape) == (20, 256) and bool(((y.float() - ref).abs() <= 1e-3 * bound + 1e-3).all())
+
+
+def test_gemv_argument_errors():
+    L = _native.lib()
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(8, 256, dtype=torch.float16, device="cuda")
+    y = torch.zeros(8, 16, dtype=torch.float32, device="cuda")
+    call = lambda t, rows, cols, batch, wbytes=4096, ydt=0: L.pfhe_quantized_gemv(t, buf.data_ptr(), wbytes, rows, cols, x.data_ptr(), batch,
+                                                                                  256, y.data_ptr(), ydt, 16, None)
+    assert call(12, 16, 256, 1) == _native.ERR_BAD_TYPE                 # a K-quant
+    assert call(2, 16, 128, 1) == _native.ERR_BAD_ARG                   # cols not a multiple of 256
+    assert call(2, 16, 256, 9) == _native.ERR_BAD_ARG                   # batch > 8
+    assert call(2, 16, 256, 1, wbytes=100) == _native.ERR_SHORT_SOURCE
+    assert call(2, 16, 256, 1, ydt=2) == _native.ERR_BAD_DTYPE          # bf16 output is not offered
+    assert call(2, 0, 256, 1) == _native.OK
