@@ -118,7 +118,7 @@ int pfhe_dequant_launch_cast2(int ggml_type, int mid_dtype, int out_dtype,
 
 /* Kernel selection and shape for experiments; zero fields mean "library default". */
 typedef struct pfhe_launch_cfg {
-    int32_t variant;      /* 0 default; 1 bulk-copy staged tiles; 2 direct global loads; 3 bulk-copy in and out; 5 one ring per warp (tile_blocks per warp, used exactly); 9 per-element fallback */
+    int32_t variant;      /* 0 default; 1 bulk-copy staged tiles shared by the CTA; 5 one ring per warp (tile_blocks per warp, used exactly); 9 per-element fallback */
     int32_t tile_blocks;  /* quant blocks per shared-memory tile (multiple of 8) */
     int32_t stages;       /* tiles in flight per CTA */
     int32_t threads;      /* threads per CTA (multiple of 32) */

@@ -100,9 +100,7 @@ using FlatFn = void (*)(const uint8_t *, void *, int64_t);
 
 struct BlockKernels {
     StagedFn staged[2];      // [streaming stores]
-    StagedFn staged_out;
     StagedFn warp_rings[2];
-    FlatFn direct[2];
     FlatFn any;
 };
 struct ElemKernels {
@@ -114,15 +112,13 @@ template <int T, int MID, int OUT> static BlockKernels block_kernels()
 {
     if constexpr (MID == OUT) {
         return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
-                            dequant_blocks_staged_out<T, MID, OUT>,
                             {dequant_blocks_warp_rings<T, MID, OUT, false>, dequant_blocks_warp_rings<T, MID, OUT, true>},
-                            {dequant_blocks_direct<T, MID, OUT, false>, dequant_blocks_direct<T, MID, OUT, true>},
                             dequant_any_alignment<T, MID, OUT>};
     } else {
         // two-step roundings only need the main kernel and the fallback; the measured
-        // alternatives (variants 2, 3, 5) are built for the plain case alone
+        // alternative (variant 5) is built for the plain case alone
         return BlockKernels{{dequant_blocks_staged<T, MID, OUT, false>, dequant_blocks_staged<T, MID, OUT, true>},
-                            nullptr, {nullptr, nullptr}, {nullptr, nullptr}, dequant_any_alignment<T, MID, OUT>};
+                            {nullptr, nullptr}, dequant_any_alignment<T, MID, OUT>};
     }
 }
 template <int T, int MID, int OUT> static ElemKernels elem_kernels()
@@ -135,7 +131,7 @@ template <int T, int MID, int OUT> static ElemKernels elem_kernels()
 template <int T, int MID, int OUT> static BlockKernels extra_kernels()
 {
     return BlockKernels{{dequant_blocks_staged<T, MID, OUT, true>, dequant_blocks_staged<T, MID, OUT, true>},
-                        nullptr, {nullptr, nullptr}, {nullptr, nullptr}, dequant_any_alignment<T, MID, OUT>};
+                        {nullptr, nullptr}, dequant_any_alignment<T, MID, OUT>};
 }
 template <int T> static bool pick_extra(int mid, int out, BlockKernels *k)
 {
@@ -337,7 +333,8 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     int variant = cfg.variant;
     if ((s % 2) || (d % 16)) variant = 9;                           // odd source or unaligned destination
 
-    if ((variant == 2 && !k.direct[ss]) || (variant == 3 && !k.staged_out) || (variant == 5 && !k.warp_rings[ss])) {
+    if (variant != 1 && variant != 5 && variant != 9) { set_error("unknown kernel variant %d", variant); return PFHE_ERR_BAD_ARG; }
+    if (variant == 5 && !k.warp_rings[ss]) {
         set_error("kernel variant %d is not built for ggml type %d", variant, ggml_type);
         return PFHE_ERR_BAD_ARG;
     }
@@ -349,16 +346,6 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
         k.any<<<(unsigned)blocks, 256, 0, stream>>>(src8, dst, n);
         return check_launch(stream, "fallback kernel launch");
     }
-    if (variant == 2) {
-        const int vec = 16 / osz;
-        const int64_t units = n / vec;
-        int64_t blocks = (units + (int64_t)cfg.threads * 4 - 1) / ((int64_t)cfg.threads * 4);
-        if (blocks < 1) blocks = 1;
-        if (blocks > max_ctas) blocks = max_ctas;
-        k.direct[ss]<<<(unsigned)blocks, cfg.threads, 0, stream>>>(src8, dst, n);
-        return check_launch(stream, "direct kernel launch");
-    }
-
     if (variant == 5) {
         // warp-private rings: tile_blocks is per warp and used exactly
         BlockKernelArgs w;
@@ -391,9 +378,8 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
     if (cfg.reserved[1] == 0) {
         // Tiles near the requested length that fill whole rounds of the grid.
-        const int out_per_block = variant == 3 ? 2 * be * osz : 0;
         const size_t per_cta = kSmemBudget / (size_t)(cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 1) - 1024;
-        int max_tile = (int)(per_cta / ((size_t)a.stages * bb + out_per_block) - 16) / 8 * 8;
+        int max_tile = (int)(per_cta / ((size_t)a.stages * bb) - 16) / 8 * 8;
         if (max_tile > 2048) max_tile = 2048;
         if (max_tile < 8) max_tile = 8;
         a.tile_blocks = balanced_tile_blocks(n_blocks, grid, a.tile_blocks, max_tile);
@@ -408,10 +394,6 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     size_t smem = (size_t)a.stages * (a.tile_blocks * bb + 16);
     if (ggml_type == T_Q4_K || ggml_type == T_Q5_K) smem += (size_t)a.tile_blocks * 8 * sizeof(float2);
     StagedFn fn = k.staged[ss];
-    if (variant == 3) {
-        smem = ((smem + 127) & ~(size_t)127) + 2 * (size_t)a.tile_blocks * be * osz;
-        fn = k.staged_out;
-    }
     if (smem > kSmemBudget) { set_error("tile configuration needs %zu bytes of shared memory", smem); return PFHE_ERR_BAD_ARG; }
     if ((rc = ensure_smem(reinterpret_cast<const void *>(fn), dev, smem))) return rc;
     fn<<<(unsigned)grid, cfg.threads, smem, stream>>>(a);

@@ -389,26 +389,6 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint3
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// 1-D bulk copy shared -> global (bulk async-group completion).
-__device__ __forceinline__ void bulk_s2g(void *gdst, const void *smem_src, uint32_t bytes)
-{
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                 ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void bulk_wait_read()
-{
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N> __device__ __forceinline__ void bulk_wait_all()
-{
-    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_smem()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 template <bool kStream> __device__ __forceinline__ void store16(void *p, uint4 v)
 {
     if constexpr (kStream) __stcs(reinterpret_cast<uint4 *>(p), v);
@@ -581,7 +561,7 @@ __device__ __forceinline__ void ring_init(StageRing &ring, uint8_t *smem, uint64
 }
 
 // ---------------------------------------------------------------------------
-// Variant 1: bulk-copy staged tiles in, coalesced 16-byte stores out, one tensor.
+// Main kernel: bulk-copy staged tiles in, coalesced 16-byte stores out, one tensor.
 // ---------------------------------------------------------------------------
 template <int T, int MID, int OUT, bool kStream>
 __global__ void __launch_bounds__(512) dequant_blocks_staged(const BlockKernelArgs a)
@@ -814,141 +794,6 @@ __global__ void __launch_bounds__(512) dequant_blocks_batch(const __grid_constan
             }
         }
         __syncthreads();
-    }
-}
-
-// ---------------------------------------------------------------------------
-// Variant 3: bulk copies in AND out.  Results are written to a shared-memory
-// output tile with 16-byte STS and leave through cp.async.bulk shared->global,
-// so the LSU only ever touches shared memory.  Only whole tiles that lie fully
-// inside n_elements take the bulk store; a ragged last tile uses direct stores.
-// ---------------------------------------------------------------------------
-template <int T, int MID, int OUT>
-__global__ void __launch_bounds__(512) dequant_blocks_staged_out(const BlockKernelArgs a)
-{
-    constexpr int BB = Fmt<T>::kBytes;
-    constexpr int VEC = 16 / OutT<OUT>::kSize;
-    constexpr int UPB = Fmt<T>::kElems / VEC;
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full[kMaxStages];
-
-    const int stage_bytes = a.tile_blocks * BB + 16;
-    const int out_tile_bytes = a.tile_blocks * Fmt<T>::kElems * OutT<OUT>::kSize;
-    uint8_t *out_smem = smem + (((size_t)a.stages * stage_bytes + 127) & ~(size_t)127);   // two buffers
-    const int64_t n_groups = (a.t.n_blocks + 7) >> 3;
-    const int64_t g0 = n_groups * blockIdx.x / gridDim.x;
-    const int64_t g1 = n_groups * (blockIdx.x + 1) / gridDim.x;
-    const int64_t b0 = g0 << 3;
-    const int64_t b1 = (g1 << 3) < a.t.n_blocks ? (g1 << 3) : a.t.n_blocks;
-    if (b1 <= b0) return;
-    const int n_tiles = (int)((b1 - b0 + a.tile_blocks - 1) / a.tile_blocks);
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    auto issue = [&](int t) {
-        const int s = t % a.stages;
-        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
-        const int64_t nb = (b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks;
-        const int64_t off = tb0 * BB;
-        int64_t bytes = (nb * BB + a.t.skew + 15) & ~(int64_t)15;
-        if (off + bytes > a.t.span_bytes) bytes = a.t.span_bytes - off;
-        mbar_expect_tx(&full[s], (uint32_t)bytes);
-        bulk_g2s(smem + (size_t)s * stage_bytes, a.t.src16 + off, (uint32_t)bytes, &full[s]);
-    };
-
-    if (threadIdx.x == 0) {
-        const int pre = n_tiles < a.stages ? n_tiles : a.stages;
-        for (int t = 0; t < pre; ++t) issue(t);
-    }
-
-    int waited_ok = 1;
-    int t = 0;
-    for (; t < n_tiles; ++t) {
-        const int s = t % a.stages;
-        const uint32_t parity = (uint32_t)(t / a.stages) & 1u;
-        if (!mbar_wait_bounded(&full[s], parity, kDeviceWaitLimitNs)) waited_ok = 0;
-        // The output buffer used two tiles ago must have been read out by its bulk store.
-        if (threadIdx.x == 0) bulk_wait_read<1>();
-        if (__syncthreads_or(!waited_ok)) break;
-
-        const uint8_t *tile = smem + (size_t)s * stage_bytes + a.t.skew;
-        uint8_t *obuf = out_smem + (size_t)(t & 1) * out_tile_bytes;
-        const int64_t tb0 = b0 + (int64_t)t * a.tile_blocks;
-        const int nb = (int)((b1 - tb0) < a.tile_blocks ? (b1 - tb0) : a.tile_blocks);
-        const int64_t e0 = tb0 * Fmt<T>::kElems;
-        const int64_t rem = a.t.n_elements - e0;
-        const int tile_elems = nb * Fmt<T>::kElems;
-        const int valid = rem < tile_elems ? (int)rem : tile_elems;
-        const int full_units = valid / VEC;
-        uint8_t *gout = reinterpret_cast<uint8_t *>(a.t.dst) + e0 * OutT<OUT>::kSize;
-        const bool bulk_ok = (valid == tile_elems);               // whole blocks only: byte count is a multiple of 64
-
-        if (bulk_ok) {
-#pragma unroll 4
-            for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
-                const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
-                *reinterpret_cast<uint4 *>(obuf + (size_t)u * 16) = r;
-            }
-            fence_proxy_async_smem();                              // make the STS visible to the async proxy
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                bulk_s2g(gout, obuf, (uint32_t)(valid * OutT<OUT>::kSize));
-                bulk_commit();
-                if (t + a.stages < n_tiles) issue(t + a.stages);
-            }
-        } else {
-            for (int u = threadIdx.x; u < full_units; u += blockDim.x) {
-                const uint4 r = decode_unit<T, MID, OUT, true>(tile + (u / UPB) * BB, u % UPB);
-                store16<false>(gout + (size_t)u * 16, r);
-            }
-            if (valid % VEC != 0 && threadIdx.x == 0) {
-                for (int e = full_units * VEC; e < valid; ++e)
-                    store_scalar<MID, OUT>(a.t.dst, e0 + e, decode_element_bytes<T>(tile, e));
-            }
-            __syncthreads();
-            if (threadIdx.x == 0 && t + a.stages < n_tiles) issue(t + a.stages);
-        }
-    }
-    if (threadIdx.x == 0) bulk_wait_all<0>();                      // stores complete before smem is released
-
-    if (t < n_tiles) {
-        if (threadIdx.x == 0) {
-            atomicExch(a.status, DEV_WAIT_TIMEOUT);
-            const int last = (t + a.stages) < n_tiles ? (t + a.stages) : n_tiles;
-            for (int k = t; k < last; ++k)
-                (void)mbar_wait_bounded(&full[k % a.stages], (uint32_t)(k / a.stages) & 1u, kDeviceWaitLimitNs / 8);
-        }
-        __syncthreads();
-    }
-}
-
-// ---------------------------------------------------------------------------
-// Variant 2: no shared memory; each thread reads its 2-byte pieces straight
-// from global memory (they hit in L1: a warp touches 144..272 contiguous bytes).
-// Source must be 2-byte aligned, destination 16-byte aligned.
-// ---------------------------------------------------------------------------
-template <int T, int MID, int OUT, bool kStream>
-__global__ void __launch_bounds__(512) dequant_blocks_direct(const uint8_t *__restrict__ src, void *__restrict__ dst,
-                                                             int64_t n_elements)
-{
-    constexpr int BB = Fmt<T>::kBytes;
-    constexpr int VEC = 16 / OutT<OUT>::kSize;
-    constexpr int UPB = Fmt<T>::kElems / VEC;
-    const int64_t full_units = n_elements / VEC;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    uint8_t *out = reinterpret_cast<uint8_t *>(dst);
-#pragma unroll 4
-    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < full_units; u += stride) {
-        const uint4 r = decode_unit<T, MID, OUT, false>(src + (u / UPB) * BB, (int)(u % UPB));
-        store16<kStream>(out + u * 16, r);
-    }
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        for (int64_t e = full_units * VEC; e < n_elements; ++e)
-            store_scalar<MID, OUT>(dst, e, decode_element_bytes<T>(src, e));
     }
 }
 

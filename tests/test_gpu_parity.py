@@ -20,11 +20,10 @@ VARIANTS = {
     "staged": {"variant": 1},
     "staged_small_tiles": {"variant": 1, "tile_blocks": 8, "stages": 2, "threads": 64, "ctas_per_sm": 1},
     "staged_deep": {"variant": 1, "tile_blocks": 1024, "stages": 8, "threads": 512, "ctas_per_sm": 1, "streaming_stores": 0},
-    "direct": {"variant": 2},
-    "staged_out": {"variant": 3, "tile_blocks": 128, "stages": 3},
     "per_element": {"variant": 9},
     "warp_rings": {"variant": 5, "tile_blocks": 64, "stages": 2, "threads": 256, "ctas_per_sm": 4},
     "warp_rings_tiny": {"variant": 5, "tile_blocks": 8, "stages": 3, "threads": 64, "ctas_per_sm": 1},
+    "staged_deep_ok": {"variant": 1, "tile_blocks": 256, "stages": 6, "threads": 512, "ctas_per_sm": 1, "streaming_stores": 0},
 }
 
 
@@ -64,7 +63,7 @@ def test_every_finite_scale_bit_pattern(fmt, dtype):
     raw = blocks.reshape(-1)
     numel = n_blocks * 32
     want = c_oracle.read_tensor(t, raw, numel, dtype, n_threads=4)
-    for variant in ("default", "direct", "staged_out"):
+    for variant in ("default", "warp_rings", "staged_deep_ok"):
         got = decode_on_gpu(t, raw, numel, dtype, cfg=VARIANTS[variant])
         assert_same_bits(to_bits(got), want, dtype, f"{fmt}->{dtype} [{variant}]")
 
@@ -76,7 +75,7 @@ def test_ragged_and_tiny_sizes(fmt, numel):
     raw = synth.random_packed(t, numel, np.random.default_rng(numel))
     for dtype in OUT_DTYPES:
         want = np_oracle.read_tensor(t, raw, numel, dtype)
-        for variant in ("default", "direct", "staged_out", "staged_small_tiles", "warp_rings", "warp_rings_tiny"):
+        for variant in ("default", "staged_small_tiles", "warp_rings", "warp_rings_tiny"):
             got = decode_on_gpu(t, raw, numel, dtype, cfg=VARIANTS[variant])
             assert_same_bits(to_bits(got), want, dtype, f"{fmt} n={numel}->{dtype} [{variant}]")
 
@@ -90,7 +89,7 @@ def test_unaligned_source(fmt, skew):
     raw = synth.random_packed(t, numel, np.random.default_rng(skew))
     for dtype in ("f16", "f32"):
         want = np_oracle.read_tensor(t, raw, numel, dtype)
-        for variant in ("default", "staged_out", "staged_small_tiles", "warp_rings"):
+        for variant in ("default", "staged_small_tiles", "warp_rings"):
             got = decode_on_gpu(t, raw, numel, dtype, skew=skew, cfg=VARIANTS[variant])
             assert_same_bits(to_bits(got), want, dtype, f"{fmt} skew={skew}->{dtype} [{variant}]")
 
@@ -141,7 +140,7 @@ def test_config2_11008x4096_to_f16(fmt, nbytes):
     raw, numel = _config_tensor(fmt, (11008, 4096), 2)
     assert raw.size == nbytes
     want = c_oracle.read_tensor(FORMATS[fmt], raw, numel, "f16", n_threads=8)
-    for variant in ("default", "direct", "staged_out"):
+    for variant in ("default", "warp_rings", "staged_deep_ok"):
         got = decode_on_gpu(FORMATS[fmt], raw, numel, "f16", cfg=VARIANTS[variant])
         assert_same_bits(to_bits(got), want, "f16", f"config 2 {fmt} [{variant}]")
 
@@ -259,7 +258,7 @@ def test_tile_schedules(schedule, exact_tiles):
 # --- opt-in ggml nibble order ---------------------------------------------------------------------
 @pytest.mark.parametrize("fmt", ["Q4_0", "Q4_1"])
 @pytest.mark.parametrize("dtype", OUT_DTYPES)
-@pytest.mark.parametrize("variant", ["default", "direct", "staged_out", "per_element", "staged_small_tiles"])
+@pytest.mark.parametrize("variant", ["default", "warp_rings", "per_element", "staged_small_tiles"])
 def test_ggml_order_golden(fmt, dtype, variant):
     import os
     from conftest import GOLDEN

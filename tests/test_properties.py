@@ -1,0 +1,60 @@
+"""Property tests (CPU): the GGUF writer and parser round-trip arbitrary metadata, and the NumPy and C
+oracles agree on arbitrary block bytes for every format."""
+import numpy as np
+from hypothesis import HealthCheck, given, settings, strategies as st
+
+from conftest import assert_same_bits
+from oracle import c_oracle, np_oracle
+from pfhe_b200 import gguf_loader as gl
+from pfhe_b200 import synth
+
+_SCALAR = st.one_of(
+    st.tuples(st.just("u8"), st.integers(0, 255)), st.tuples(st.just("i8"), st.integers(-128, 127)),
+    st.tuples(st.just("u16"), st.integers(0, 65535)), st.tuples(st.just("i32"), st.integers(-2**31, 2**31 - 1)),
+    st.tuples(st.just("u64"), st.integers(0, 2**64 - 1)), st.tuples(st.just("i64"), st.integers(-2**63, 2**63 - 1)),
+    st.tuples(st.just("bool"), st.booleans()), st.tuples(st.just("str"), st.text(max_size=40)),
+    st.tuples(st.just("f64"), st.floats(allow_nan=False)),
+    st.tuples(st.just("f32"), st.floats(width=32, allow_nan=False)))
+_ARRAY = st.one_of(
+    st.tuples(st.just("arr:str"), st.lists(st.text(max_size=12), max_size=300)),
+    st.tuples(st.just("arr:i32"), st.lists(st.integers(-2**31, 2**31 - 1), max_size=50)),
+    st.tuples(st.just("arr:bool"), st.lists(st.booleans(), max_size=20)),
+    st.tuples(st.just("arr:arr:u16"), st.lists(st.lists(st.integers(0, 65535), max_size=4), max_size=5)))
+
+
+@settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@given(entries=st.lists(st.tuples(st.text(min_size=1, max_size=20), st.one_of(_SCALAR, _ARRAY)), max_size=8, unique_by=lambda e: e[0]),
+       shapes=st.lists(st.tuples(st.integers(1, 5), st.integers(1, 3)), min_size=1, max_size=4))
+def test_writer_parser_roundtrip(tmp_path, entries, shapes):
+    meta = [(k, kind, v) for k, (kind, v) in entries]
+    specs = [synth.TensorSpec(f"t{i}.weight", (r, 32 * c), (2, 3, 8, 6, 0)[i % 5]) for i, (r, c) in enumerate(shapes)]
+    path = tmp_path / "p.gguf"
+    size = synth.write_gguf(path, specs, meta, seed=1)
+    with gl.GGUFReader(path) as r:
+        assert list(r.metadata) == [k for k, _, _ in meta]
+        for k, kind, v in meta:
+            got = r.metadata[k]
+            if kind == "f32":
+                assert np.float32(got) == np.float32(v)
+            else:
+                assert got == v, (k, kind)
+        assert [(t.name, t.shape, t.dtype) for t in r.tensors.values()] == [(s.name, s.shape, s.ggml_type) for s in specs]
+        last = list(r.tensors.values())[-1]
+        assert r.header.tensor_data_offset + last.offset + last.nbytes == size
+
+
+@settings(max_examples=60, deadline=None)
+@given(t=st.sampled_from([2, 3, 8, 6, 7, 10, 11, 12, 13, 14, 2 | 0x100, 3 | 0x100]), n_blocks=st.integers(1, 6),
+       seed=st.integers(0, 2**32 - 1), cut=st.integers(0, 31), dtype=st.sampled_from(["f32", "f16", "bf16"]))
+def test_oracles_agree_on_arbitrary_finite_blocks(t, n_blocks, seed, cut, dtype):
+    be, bb = np_oracle.BLOCK_GEOMETRY[t & 0xFF]
+    rng = np.random.default_rng(seed)
+    blocks = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+    fields = {2: (0,), 3: (0, 2), 8: (0,)}.get(t & 0xFF) or synth._F16_FIELDS[t & 0xFF]
+    for off in fields:                                  # keep the fp16 fields finite: NaN payloads are not compared
+        h = blocks[:, off:off + 2].copy().view(np.uint16).reshape(-1)
+        h = np.where((h & 0x7C00) == 0x7C00, h & 0xBFFF, h).astype(np.uint16)
+        blocks[:, off:off + 2] = h.view(np.uint8).reshape(n_blocks, 2)
+    numel = max(1, n_blocks * be - cut)
+    raw = blocks.reshape(-1)
+    assert_same_bits(c_oracle.read_tensor(t, raw, numel, dtype), np_oracle.read_tensor(t, raw, numel, dtype), dtype, f"type {t}")
