@@ -287,6 +287,16 @@ int pfhe_loader_submit_fd(pfhe_loader *ld, int fd, int64_t file_offset, int64_t 
                           void *stream);
 
 /*
+ * Copy `bytes` of packed data from ordinary host memory into device memory
+ * UNDECODED, through the same pinned ring (for weights that stay quantised on
+ * the GPU).  Replaces StreamingGGUFLoader.stream_tensor_raw of the reference
+ * (src/phfe/inference/gguf_cuda.py:231-241), which copies from a pageable
+ * bytes object.  Work queued on `stream` afterwards sees the bytes; host_src may
+ * be released when the call returns.
+ */
+int pfhe_loader_upload(pfhe_loader *ld, const void *host_src, int64_t bytes, void *dst_dev, void *stream);
+
+/*
  * Block until everything submitted so far has finished on the device, or until
  * timeout_ms has passed (PFHE_ERR_TIMEOUT).  Also reports a device-side wait
  * failure (PFHE_ERR_DEVICE_WAIT).

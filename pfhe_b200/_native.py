@@ -27,7 +27,7 @@ EXPORTED_SYMBOLS = (
     "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes", "pfhe_scan_string_array",
     "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex", "pfhe_dequant_launch_batch", "pfhe_dequant_launch_batch_ex",
     "pfhe_dequant_from_host_noalloc", "pfhe_device_status", "pfhe_launch_count", "pfhe_selftest_bounded_wait", "pfhe_quantized_gemv",
-    "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd",
+    "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd", "pfhe_loader_upload",
     "pfhe_loader_wait", "pfhe_loader_get_stats", "pfhe_loader_destroy",
 )
 
@@ -95,6 +95,8 @@ def lib() -> ctypes.CDLL:
     L.pfhe_loader_submit.argtypes = [vp, vp, i64, i32, i32, i32, vp, i64, i64, vp]
     L.pfhe_loader_submit_fd.restype = i32
     L.pfhe_loader_submit_fd.argtypes = [vp, i32, i64, i64, i32, i32, i32, vp, i64, i64, vp]
+    L.pfhe_loader_upload.restype = i32
+    L.pfhe_loader_upload.argtypes = [vp, vp, i64, vp, vp]
     L.pfhe_loader_wait.restype = i32
     L.pfhe_loader_wait.argtypes = [vp, i32]
     L.pfhe_loader_get_stats.restype = i32

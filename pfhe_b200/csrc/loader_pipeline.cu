@@ -298,6 +298,46 @@ int pfhe_loader_submit_fd(pfhe_loader *ld, int fd, int64_t file_offset, int64_t 
                        static_cast<cudaStream_t>(stream));
 }
 
+int pfhe_loader_upload(pfhe_loader *ld, const void *host_src, int64_t bytes, void *dst_dev, void *stream_)
+{
+    if (!ld) { set_error("null loader"); return PFHE_ERR_BAD_ARG; }
+    if (bytes < 0) { set_error("negative size"); return PFHE_ERR_BAD_ARG; }
+    if (bytes == 0) return PFHE_OK;
+    if (!host_src || !dst_dev) { set_error("null pointer"); return PFHE_ERR_BAD_ARG; }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    std::lock_guard<std::mutex> lk(ld->mu);
+    DeviceGuard guard;
+    int rc = guard.enter(ld->device);
+    if (rc) return rc;
+    Source src;
+    src.host = static_cast<const uint8_t *>(host_src);
+    ld->stats.tensors++;
+    for (int64_t off = 0; off < bytes; off += ld->slot_bytes) {
+        const int64_t nb = (bytes - off) < ld->slot_bytes ? (bytes - off) : ld->slot_bytes;
+        Slot &s = ld->slots[ld->next_slot];
+        ld->next_slot = (ld->next_slot + 1) % (int)ld->slots.size();
+        if (s.in_use) {
+            const auto t0 = Clock::now();
+            rc = wait_event_bounded(s.done, ld->slot_timeout_ms, "waiting for a free staging slot");
+            ld->stats.slot_wait_seconds += seconds_since(t0);
+            if (rc) return rc;
+        }
+        const auto t0 = Clock::now();
+        if ((rc = fill_pinned(ld, s.pinned, src, off, nb))) return rc;
+        ld->stats.host_copy_seconds += seconds_since(t0);
+        // pinned slot -> destination directly: the packed bytes are the result, no device staging
+        cudaError_t e = cudaMemcpyAsync(static_cast<uint8_t *>(dst_dev) + off, s.pinned, (size_t)nb, cudaMemcpyHostToDevice,
+                                        ld->copy_stream);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(H2D)");
+        if ((e = cudaEventRecord(s.done, ld->copy_stream)) != cudaSuccess) return cuda_fail(e, "cudaEventRecord(done)");
+        if ((e = cudaStreamWaitEvent(stream, s.done, 0)) != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+        s.in_use = true;
+        ld->stats.bytes_staged += nb;
+        ld->stats.chunks++;
+    }
+    return PFHE_OK;
+}
+
 int pfhe_loader_wait(pfhe_loader *ld, int timeout_ms)
 {
     if (!ld) { set_error("null loader"); return PFHE_ERR_BAD_ARG; }

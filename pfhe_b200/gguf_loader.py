@@ -507,6 +507,22 @@ class GGUFReader:
             return out
         return target if want.type == "cuda" else target.to(want)
 
+    def read_tensor_packed(self, name: str, device: str = "cuda") -> torch.Tensor:
+        """The tensor's packed bytes on the GPU, undecoded, as a uint8 tensor (for weights that stay
+        quantised: ``pfhe_b200.quantized``).  Takes over ``StreamingGGUFLoader.stream_tensor_raw`` of the
+        reference (src/phfe/inference/gguf_cuda.py:231-241); the bytes go through the pinned ring."""
+        info, start, nbytes = self._extent(name)
+        _, cuda_dev = _cuda_device_for(device)
+        if start + nbytes > len(self._mmap):
+            raise ValueError(f"Data too short: {max(len(self._mmap) - start, 0)} < {nbytes}")
+        out = torch.empty(nbytes, dtype=torch.uint8, device=cuda_dev)
+        if nbytes:
+            with torch.cuda.device(cuda_dev):
+                stager = _Stager.get(cuda_dev.index)
+                _native.check(_native.lib().pfhe_loader_upload(stager.handle, self._host_address(start, nbytes), nbytes,
+                                                               out.data_ptr(), torch.cuda.current_stream(cuda_dev).cuda_stream))
+        return out
+
     def tensor_iterator(self, pattern: Optional[str] = None, device: str = "cpu",
                         dtype: torch.dtype = torch.float32) -> Iterator[Tuple[str, torch.Tensor]]:
         """(name, tensor) pairs in file order, optionally filtered by a glob (reference :381-400)."""

@@ -57,6 +57,15 @@ class QuantizedTensor:
         return self.numel * 2 / self.nbytes
 
 
+def load_quantized_linear(reader, name: str, device: str = "cuda", bias: Optional[torch.Tensor] = None) -> "QuantizedLinear":
+    """A ``QuantizedLinear`` whose packed weight is tensor ``name`` of an opened ``GGUFReader``."""
+    info = reader.tensors[name]
+    if len(info.shape) != 2:
+        raise ValueError(f"{name} has shape {info.shape}; a linear weight needs two axes")
+    raw = reader.read_tensor_packed(name, device=device)
+    return QuantizedLinear(info.shape[1], info.shape[0], info.dtype, raw, bias=bias, nibble_order=reader.nibble_order)
+
+
 def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int, int], quant_type: int,
                      nibble_order: str = "reference") -> torch.Tensor:
     """``x @ W.T`` for packed ``W`` of logical shape ``(out_features, in_features)``; returns fp16.

@@ -99,3 +99,38 @@ def test_gemv_argument_errors():
     assert call(2, 16, 256, 1, wbytes=100) == _native.ERR_SHORT_SOURCE
     assert call(2, 16, 256, 1, ydt=2) == _native.ERR_BAD_DTYPE          # bf16 output is not offered
     assert call(2, 0, 256, 1) == _native.OK
+
+
+def test_packed_upload_and_linear_from_file(tmp_path):
+    """read_tensor_packed moves the file's bytes to the GPU unchanged (through the pinned ring, in
+    chunks), and a QuantizedLinear built from them multiplies like the decoded weight."""
+    from pfhe_b200 import gguf_loader as gl
+    from pfhe_b200.quantized import load_quantized_linear
+    path = tmp_path / "q.gguf"
+    specs = [synth.TensorSpec("a.weight", (768, 1024), 2), synth.TensorSpec("b.weight", (100, 512), 12), synth.TensorSpec("n.weight", (64,), 0)]
+    synth.write_gguf(path, specs, seed=3)
+    old = gl._Stager.slot_bytes, dict(gl._Stager._by_device)
+    gl._Stager.shutdown()
+    gl._Stager.slot_bytes = 100_000                      # several chunks per tensor
+    try:
+        with gl.GGUFReader(path) as r:
+            for n in r.tensors:
+                packed = r.read_tensor_packed(n)
+                assert packed.dtype == torch.uint8 and packed.is_cuda
+                assert bytes(packed.cpu().numpy().tobytes()) == r.read_tensor_raw(n)
+            lin = load_quantized_linear(r, "a.weight")
+            w = r.read_tensor("a.weight", device="cuda", dtype=torch.float16).float()
+            lin_k = load_quantized_linear(r, "b.weight")                      # a K-quant weight: decode-then-linear path
+            wk = r.read_tensor("b.weight", device="cuda", dtype=torch.float16).float()
+            with pytest.raises(ValueError):
+                load_quantized_linear(r, "n.weight")
+        x = torch.randn(3, 1024, device="cuda").half()
+        ref = x.float() @ w.T
+        bound = x.float().abs() @ w.abs().T
+        assert bool(((lin(x).float() - ref).abs() <= 2e-5 * bound + ref.abs() * 2 ** -10 + 1e-7).all())
+        xk = torch.randn(2, 512, device="cuda").half()
+        refk = xk.float() @ wk.T
+        assert bool(((lin_k(xk).float() - refk).abs() <= 1e-3 * (xk.float().abs() @ wk.abs().T) + 1e-3).all())
+    finally:
+        gl._Stager.shutdown()
+        gl._Stager.slot_bytes = old[0]
