@@ -584,6 +584,33 @@ def run_e2e(args, rank, dev, host_raw, dsts, pfhe_b200, synth, gl, torch):
             pass
 
 
+def run_gemv_case(parts) -> None:
+    """GEMV:FORMAT:ROWS:COLS:BATCH[:LAUNCHES] -- a few launches of pfhe_quantized_gemv (for profilers)."""
+    import torch
+    from pfhe_b200 import _native
+    fmt = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8}[parts[1]]
+    rows, cols, batch = int(parts[2]), int(parts[3]), int(parts[4])
+    launches = int(parts[5]) if len(parts) > 5 else 6
+    L = _native.lib()
+    nb = L.pfhe_tensor_nbytes(fmt, rows * cols)
+    ws = [torch.randint(0, 255, (nb,), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    x = torch.randn(batch, cols, device="cuda").half()
+    y = torch.empty(batch, rows, dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream()
+    evs = []
+    for i in range(launches):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(st)
+        _native.check(L.pfhe_quantized_gemv(fmt, ws[i & 1].data_ptr(), nb, rows, cols, x.data_ptr(), batch, cols, y.data_ptr(),
+                                            _native.OUT_F16, rows, st.cuda_stream))
+        b.record(st)
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    ms = sorted(a.elapsed_time(b) for a, b in evs[1:])[len(evs[1:]) // 2]
+    print(json.dumps({"kernel_case": ":".join(parts), "packed_bytes": nb, "median_ms": ms, "packed_gbps": nb / ms / 1e6}), flush=True)
+
+
 def run_kernel_case(spec: str) -> None:
     """A few launches of one decode kernel on device-resident data (the case profilers capture).
 
@@ -593,6 +620,8 @@ def run_kernel_case(spec: str) -> None:
     import torch
     from pfhe_b200 import _native, synth
     parts = spec.split(":")
+    if parts[0] == "GEMV":
+        return run_gemv_case(parts)
     fmt = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8, "F16": 1, "BF16": 30, "F32": 0}[parts[0]]
     oid, odt = {"f32": (0, torch.float32), "f16": (1, torch.float16), "bf16": (2, torch.bfloat16)}[parts[1]]
     numel = int(parts[2])
