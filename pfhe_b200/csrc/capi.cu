@@ -5,6 +5,7 @@
 #include "dequant_kernels.cuh"
 
 #include <atomic>
+#include <limits.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -219,19 +220,21 @@ static int balanced_tile_blocks(int64_t n_blocks, int64_t grid, int target, int 
     return (int)(tg * 8);
 }
 
-// Default kernel shapes, chosen from sweeps on B200 (148 SMs, HBM3e).  What the
-// sweeps showed: two stages beat deeper rings (reads that run far ahead of the
-// writes cost DRAM efficiency), two or three CTAs per SM beat full occupancy,
-// and an output tile of about 32 KB per CTA is the sweet spot.
-struct Shape { int tile_blocks, stages, threads, ctas_per_sm; };
+// Default kernel shapes, chosen from sweeps on B200 (148 SMs, HBM3e).  The decisive finding: a
+// NON-persistent grid -- one tile per CTA, CTAs dispatched in order by the hardware -- keeps the
+// whole GPU's write frontier one compact, advancing window and reaches 6.5-6.7 TB/s, where
+// persistent CTAs looping over tiles (any schedule, any ring depth) level off at 5.9-6.3 TB/s; a
+// plain fill kernel shows the same gap (7.46 vs 6.3 TB/s).  So by default ctas_per_sm = 0 means
+// "grid = number of tiles, one stage"; a positive ctas_per_sm selects the persistent form.
+struct Shape { int tile_blocks, threads; };
 
 static Shape default_shape(int ggml_type, int out_dtype)
 {
-    if (ggml_type >= T_Q2_K && ggml_type <= T_Q6_K)                 // 256-element blocks: same 32 KB output tile
-        return out_dtype == O_F32 ? Shape{32, 2, 256, 2} : Shape{64, 2, 256, 2};
-    if (out_dtype == O_F32) return Shape{256, 2, 256, 2};
-    if (ggml_type == T_Q8_0) return Shape{256, 2, 256, 3};
-    return Shape{512, 2, 256, 2};
+    const int base = ggml_type & ~T_ORDER_FLAG;
+    // about 16 sixteen-byte stores per thread measured best (8 to 16 are within 1 %)
+    if (base >= T_Q2_K && base <= T_Q6_K)                           // 256-element blocks
+        return out_dtype == O_F32 ? Shape{32, 128} : Shape{64, 128};
+    return out_dtype == O_F32 ? Shape{256, 256} : Shape{512, 128};
 }
 
 static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
@@ -239,8 +242,8 @@ static void default_cfg(int ggml_type, int out_dtype, pfhe_launch_cfg *c)
     const Shape d = default_shape(ggml_type, out_dtype);
     if (c->variant == 0) c->variant = 1;
     if (c->threads <= 0) c->threads = d.threads;
-    if (c->stages <= 0) c->stages = d.stages;
-    if (c->ctas_per_sm <= 0) c->ctas_per_sm = d.ctas_per_sm;
+    if (c->ctas_per_sm < 0) c->ctas_per_sm = 0;
+    if (c->stages <= 0) c->stages = c->ctas_per_sm > 0 ? 2 : 1;
     if (c->tile_blocks <= 0) c->tile_blocks = d.tile_blocks;
     if (c->streaming_stores < 0) c->streaming_stores = 1;
 }
@@ -288,7 +291,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     const int ss = cfg.streaming_stores ? 1 : 0;
     const uintptr_t s = reinterpret_cast<uintptr_t>(src), d = reinterpret_cast<uintptr_t>(dst);
     const uint8_t *src8 = static_cast<const uint8_t *>(src);
-    const int max_ctas = sms * cfg.ctas_per_sm;
+    const int64_t max_ctas = (int64_t)sms * (cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 2);
 
     if (be == 1) {                                                  // F32 / F16 / BF16 input
         ElemKernels k;
@@ -299,12 +302,13 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
         if (!ok) { set_error("no kernel"); return PFHE_ERR_BAD_DTYPE; }
         const bool fast = cfg.variant != 9 && (s % 16 == 0) && (d % 16 == 0);
         if (fast) {
+            // one CTA per 4 x threads vector steps, as many CTAs as that takes (no grid-stride loop)
             const int wide = bb > osz ? bb : osz;
             const int64_t steps = n / (16 / wide);
-            int64_t blocks = (steps + (int64_t)cfg.threads * 4 - 1) / ((int64_t)cfg.threads * 4);
+            const int threads = 256;
+            int64_t blocks = (steps + (int64_t)threads * 4 - 1) / ((int64_t)threads * 4);
             if (blocks < 1) blocks = 1;
-            if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
-            k.vec[ss]<<<(unsigned)blocks, cfg.threads, 0, stream>>>(src8, dst, n);
+            k.vec[ss]<<<(unsigned)blocks, threads, 0, stream>>>(src8, dst, n);
         } else {
             int64_t blocks = (n + 255) / 256;
             if (blocks > (int64_t)sms * 16) blocks = (int64_t)sms * 16;
@@ -375,8 +379,14 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
 
     // Small tensors: fewer CTAs, so every CTA has at least one 8-block group.
     const int64_t n_groups = (n_blocks + 7) / 8;
-    const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
-    if (cfg.reserved[1] == 0) {
+    int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
+    if (cfg.ctas_per_sm <= 0) {
+        // default: one tile per CTA, as many CTAs as tiles
+        if ((int64_t)a.tile_blocks > n_groups * 8) a.tile_blocks = (int)(n_groups * 8);
+        grid = (n_blocks + a.tile_blocks - 1) / a.tile_blocks;
+        a.stages = 1;
+        a.interleaved = 1;
+    } else if (cfg.reserved[1] == 0) {
         // Tiles near the requested length that fill whole rounds of the grid.
         const size_t per_cta = kSmemBudget / (size_t)(cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 1) - 1024;
         int max_tile = (int)(per_cta / ((size_t)a.stages * bb) - 16) / 8 * 8;
@@ -384,8 +394,10 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
         if (max_tile < 8) max_tile = 8;
         a.tile_blocks = balanced_tile_blocks(n_blocks, grid, a.tile_blocks, max_tile);
     } else {
-        const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
-        if (groups_per_cta * 8 < a.tile_blocks) a.tile_blocks = (int)(groups_per_cta * 8);
+        // exact tiles: never more CTAs than tiles
+        if ((int64_t)a.tile_blocks > n_groups * 8) a.tile_blocks = (int)(n_groups * 8);
+        const int64_t exact_tiles = (n_blocks + a.tile_blocks - 1) / a.tile_blocks;
+        if (grid > exact_tiles) grid = exact_tiles;
     }
     const int64_t tiles = (n_blocks + a.tile_blocks - 1) / a.tile_blocks;
     const int64_t tiles_per_cta = (tiles + grid - 1) / grid;
@@ -418,7 +430,7 @@ static int launch_batch_kernel(const pfhe_tensor_desc *d, const int *idx, int co
     }
     const Shape ds = default_shape(d[idx[lead]].ggml_type, d[idx[lead]].out_dtype);
     const int threads = cfg && cfg->threads > 0 ? cfg->threads : ds.threads;
-    const int cps = cfg && cfg->ctas_per_sm > 0 ? cfg->ctas_per_sm : ds.ctas_per_sm;
+    const int cps = cfg && cfg->ctas_per_sm > 0 ? cfg->ctas_per_sm : 0;      // 0: one tile per CTA
     const int target = cfg && cfg->tile_blocks > 0 ? cfg->tile_blocks : ds.tile_blocks;
     BatchKernelArgs a;
     memset(&a, 0, sizeof a);
@@ -432,27 +444,34 @@ static int launch_batch_kernel(const pfhe_tensor_desc *d, const int *idx, int co
         blocks += a.t[i].n_blocks;
     }
     a.n_tensors = count;
-    a.stages = cfg && cfg->stages > 0 ? cfg->stages : ds.stages;
+    a.stages = cps > 0 ? (cfg && cfg->stages > 0 ? cfg->stages : 2) : 1;
     int rc;
     if ((rc = status_word(dev, &a.status))) return rc;
-    const int64_t max_ctas = (int64_t)sms * cps;
     const int64_t groups = (blocks + 7) / 8;
-    const int64_t grid = groups < max_ctas ? groups : max_ctas;
-    int max_tile = (int)((kSmemBudget / (size_t)cps - 1024) / ((size_t)a.stages * 34) - 16) / 8 * 8;
-    if (max_tile > 2048) max_tile = 2048;
-    a.tile_blocks = balanced_tile_blocks(blocks, grid, target, max_tile);
+    int64_t grid;
+    if (cps > 0) {
+        const int64_t max_ctas = (int64_t)sms * cps;
+        grid = groups < max_ctas ? groups : max_ctas;
+        int max_tile = (int)((kSmemBudget / (size_t)cps - 1024) / ((size_t)a.stages * 34) - 16) / 8 * 8;
+        if (max_tile > 2048) max_tile = 2048;
+        a.tile_blocks = balanced_tile_blocks(blocks, grid, target, max_tile);
+    } else {
+        a.tile_blocks = target;
+        grid = LLONG_MAX;                                           // set to the tile count below
+    }
     int64_t tiles = 0;
     for (int i = 0; i < count; ++i) {
         a.tile_prefix[i] = tiles;
         tiles += (a.t[i].n_blocks + a.tile_blocks - 1) / a.tile_blocks;
     }
     a.tile_prefix[count] = tiles;
+    if (grid > tiles) grid = tiles;
     const int64_t tiles_per_cta = (tiles + grid - 1) / grid;
     if (tiles_per_cta < a.stages) a.stages = (int)tiles_per_cta;
     const size_t smem = (size_t)a.stages * (a.tile_blocks * 34 + 16);
     auto fn = dequant_blocks_batch<true>;
     if ((rc = ensure_smem(reinterpret_cast<const void *>(fn), dev, smem))) return rc;
-    fn<<<(unsigned)(tiles < grid ? tiles : grid), threads, smem, stream>>>(a);
+    fn<<<(unsigned)grid, threads, smem, stream>>>(a);
     return check_launch(stream, "batch kernel launch");
 }
 

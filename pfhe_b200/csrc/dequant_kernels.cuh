@@ -799,7 +799,7 @@ __global__ void __launch_bounds__(512) dequant_blocks_batch(const __grid_constan
 
 // ---------------------------------------------------------------------------
 // Element-wise formats (F32 / F16 / BF16 in).  Each thread moves 16 bytes of the
-// wider side with one vector access.  Both pointers 16-byte aligned.
+// wider side with one vector access, four times.  Both pointers 16-byte aligned.
 // ---------------------------------------------------------------------------
 template <int T> __device__ __forceinline__ float widen16(uint32_t bits)
 {
@@ -825,10 +825,14 @@ __global__ void __launch_bounds__(512) convert_elements(const uint8_t *__restric
     constexpr int WIDE = IN_SZ > OUT_SZ ? IN_SZ : OUT_SZ;
     constexpr int EPT = 16 / WIDE;                                 // elements per thread step: 8 (2->2) or 4
     const int64_t n_steps = n_elements / EPT;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     uint8_t *out = reinterpret_cast<uint8_t *>(dst);
-#pragma unroll 4
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_steps; i += stride) {
+    // One CTA covers 4 x blockDim consecutive vector steps and then exits: with as many CTAs as that
+    // takes, the hardware's in-order CTA dispatch keeps all reads and writes in one advancing window.
+    const int64_t cta_base = (int64_t)blockIdx.x * blockDim.x * 4;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int64_t i = cta_base + (int64_t)k * blockDim.x + threadIdx.x;
+        if (i >= n_steps) break;
         if constexpr (IN_SZ == 2 && OUT_SZ == 2) {
             uint4 v = __ldcs(reinterpret_cast<const uint4 *>(src) + i);
             v.x = convert_pair16<T, MID, OUT>(v.x); v.y = convert_pair16<T, MID, OUT>(v.y);

@@ -66,27 +66,26 @@ void launch_blocks(const uint8_t *src, void *dst, int64_t n, int *status, int sm
     a.t.n_blocks = (n + Fmt<T>::kElems - 1) / Fmt<T>::kElems;
     a.t.span_bytes = (a.t.n_blocks * Fmt<T>::kBytes + 15) & ~(int64_t)15;
     a.t.kind = 0;
-    a.stages = 2;
+    a.stages = 1;                                              // one tile per CTA, CTAs dispatched in order
     a.interleaved = 1;
     a.status = status;
+    (void)sms;
     const int64_t n_groups = (a.t.n_blocks + 7) / 8;
-    const int64_t max_ctas = (int64_t)sms * 2;
-    const int64_t grid = n_groups < max_ctas ? n_groups : max_ctas;
-    const int64_t groups_per_cta = (n_groups + grid - 1) / grid;
-    const int target = (OUT == O_F32 ? 8192 : 16384) / Fmt<T>::kElems;   // 34.8 KB of shared memory at most: no opt-in needed
-    a.tile_blocks = groups_per_cta * 8 < target ? (int)(groups_per_cta * 8) : target;
+    const int target = (OUT == O_F32 ? 4096 : 16384) / Fmt<T>::kElems;  // 16 stores per thread; under 18 KB of shared memory
+    a.tile_blocks = n_groups * 8 < target ? (int)(n_groups * 8) : target;
+    const int64_t grid = (a.t.n_blocks + a.tile_blocks - 1) / a.tile_blocks;
     const size_t smem = (size_t)a.stages * (a.tile_blocks * Fmt<T>::kBytes + 16) +
                         (size_t)a.tile_blocks * ScaleTable<T>::kGroups * sizeof(float2);
-    dequant_blocks_staged<T, OUT, OUT, true><<<(unsigned)grid, 256, smem, stream>>>(a);
+    dequant_blocks_staged<T, OUT, OUT, true><<<(unsigned)grid, 128, smem, stream>>>(a);
 }
 
 template <int T, int OUT>
 void launch_elements(const uint8_t *src, void *dst, int64_t n, int sms, cudaStream_t stream)
 {
     constexpr int wide = Fmt<T>::kBytes > OutT<OUT>::kSize ? Fmt<T>::kBytes : OutT<OUT>::kSize;
-    int64_t blocks = (n / (16 / wide) + 1023) / 1024;
+    int64_t blocks = (n / (16 / wide) + 1023) / 1024;       // 4 x 256 vector steps per CTA
     if (blocks < 1) blocks = 1;
-    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    (void)sms;
     convert_elements<T, OUT, OUT, true><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n);
 }
 
