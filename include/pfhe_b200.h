@@ -120,12 +120,12 @@ int pfhe_dequant_launch_cast2(int ggml_type, int mid_dtype, int out_dtype,
 typedef struct pfhe_launch_cfg {
     int32_t variant;      /* 0 default; 1 bulk-copy staged tiles shared by the CTA; 5 one ring per warp (tile_blocks per warp, used exactly); 9 per-element fallback */
     int32_t tile_blocks;  /* quant blocks per shared-memory tile (multiple of 8) */
-    int32_t stages;       /* tiles in flight per CTA */
+    int32_t stages;       /* tiles in flight per CTA (persistent grid only; a one-tile CTA uses 1) */
     int32_t threads;      /* threads per CTA (multiple of 32) */
-    int32_t ctas_per_sm;  /* grid = SM count * ctas_per_sm */
+    int32_t ctas_per_sm;  /* 0 (default): one tile per CTA, grid = tile count; > 0: persistent grid of SM count * ctas_per_sm */
     int32_t streaming_stores; /* 1: evict-first stores; 0: default; -1: library default */
-    int32_t reserved[2];  /* [0]: 0/2 = tiles dealt round-robin to the CTAs (default), 1 = one contiguous run per CTA;
-                             [1]: 0 = tile_blocks is a target, adjusted so the tiles fill whole rounds of the grid,
+    int32_t reserved[2];  /* [0] (persistent grid): 0/2 = tiles dealt round-robin to the CTAs, 1 = one contiguous run per CTA;
+                             [1] (persistent grid): 0 = tile_blocks is a target, adjusted so the tiles fill whole rounds of the grid,
                                   1 = use tile_blocks exactly */
 } pfhe_launch_cfg;
 
