@@ -214,10 +214,13 @@ int pfhe_device_status(int device);
  * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER) and decoded on the
  * fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
  * (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight
- * to fp16 in device memory and then call F.linear.  Every weight takes exactly
- * the fp16 value pfhe_dequant_launch(..., PFHE_OUT_F16) gives it, x is fp16,
- * products and sums are fp32; the result differs from an fp32 reference only by
- * summation order.  cols must be a multiple of 256; w_dev and x_dev 16-byte
+ * to fp16 in device memory and then call F.linear.  Every Q4_0 / Q8_0 weight
+ * takes exactly the fp16 value pfhe_dequant_launch(..., PFHE_OUT_F16) gives it;
+ * a Q4_1 weight is q*d + m rounded once to fp16 (the decode kernels round to
+ * fp32 first, one fp16 ulp apart in rare double-rounding cases).  x is fp16,
+ * products and sums are fp32; the result differs from an fp32 reference on the
+ * decoded weights by summation order (and, for Q4_1, by those rare ulps).
+ * cols must be a multiple of 256; w_dev and x_dev 16-byte
  * aligned; x is [batch][ldx] halves, y is [batch][ldy] of y_dtype (PFHE_OUT_F32
  * or PFHE_OUT_F16).
  */

@@ -264,14 +264,26 @@ class GGUFReader:
             w = reader.read_tensor("blk.0.attn_q.weight", device="cuda", dtype=torch.float16)
     """
 
-    def __init__(self, path: str | Path, *, nibble_order: str = "reference"):
+    def __init__(self, path: str | Path, *, nibble_order: str = "reference",
+                 alignment: int | str = "reference"):
         """nibble_order: "reference" decodes Q4_0/Q4_1 as the reference does (byte j of a block
         gives elements 2j and 2j+1); "ggml" uses ggml's own order (low nibbles are elements
-        0..15, high nibbles 16..31), which is what files written by llama.cpp contain."""
+        0..15, high nibbles 16..31), which is what files written by llama.cpp contain.
+
+        alignment: where the tensor data section starts.  "reference" rounds the end of the
+        header up to 32 bytes whatever the file says, as the reference does (:321-323);
+        "metadata" uses the file's ``general.alignment`` key (32 when absent), which is what
+        the GGUF format specifies; an integer forces that value."""
         if nibble_order not in ("reference", "ggml"):
             raise ValueError(f"nibble_order must be 'reference' or 'ggml', not {nibble_order!r}")
+        if isinstance(alignment, str):
+            if alignment not in ("reference", "metadata"):
+                raise ValueError(f"alignment must be 'reference', 'metadata' or an integer, not {alignment!r}")
+        elif isinstance(alignment, bool) or not isinstance(alignment, int) or alignment <= 0:
+            raise ValueError(f"alignment must be 'reference', 'metadata' or a positive integer, not {alignment!r}")
         self.path = Path(path)
         self.nibble_order = nibble_order
+        self.alignment = alignment
         self._file = None
         self._mmap = None
         self._view: Optional[np.ndarray] = None      # uint8 view of the mmap (for host addresses)
@@ -419,7 +431,14 @@ class GGUFReader:
             hdr.tensors[name] = GGUFTensorInfo(name=name, n_dims=n_dims, dims=tuple(dims), dtype=ggml_type,
                                                offset=offset)
         # The reference aligns the data section to a fixed 32 bytes (:321-323).
-        hdr.tensor_data_offset = (self._cursor + 31) // 32 * 32
+        align = 32
+        if self.alignment == "metadata":
+            align = hdr.metadata.get("general.alignment", 32)
+            if isinstance(align, bool) or not isinstance(align, int) or align <= 0:
+                raise ValueError(f"Invalid general.alignment: {align!r}")
+        elif isinstance(self.alignment, int):
+            align = self.alignment
+        hdr.tensor_data_offset = (self._cursor + align - 1) // align * align
 
     # -- raw bytes ------------------------------------------------------------
     def _extent(self, name: str) -> Tuple[GGUFTensorInfo, int, int]:
@@ -537,9 +556,10 @@ class GGUFReader:
 # ---------------------------------------------------------------------------
 @contextmanager
 def tensor_loading_context(path: str | Path, device: str = "cpu",
-                           dtype: torch.dtype = torch.float32, *, nibble_order: str = "reference") -> Iterator[GGUFReader]:
+                           dtype: torch.dtype = torch.float32, *, nibble_order: str = "reference",
+                           alignment: int | str = "reference") -> Iterator[GGUFReader]:
     """Yields an opened reader.  ``device``/``dtype`` are accepted and unused, as in the reference (:561-575)."""
-    with GGUFReader(path, nibble_order=nibble_order) as reader:
+    with GGUFReader(path, nibble_order=nibble_order, alignment=alignment) as reader:
         yield reader
 
 
@@ -547,16 +567,18 @@ class StreamingDequantizer:
     """Streams decoded tensors to the GPU in batches (reference :603-660)."""
 
     def __init__(self, path: str | Path, batch_size: int = 4, device: str = "cuda",
-                 dtype: torch.dtype = torch.float16, *, nibble_order: str = "reference"):
+                 dtype: torch.dtype = torch.float16, *, nibble_order: str = "reference",
+                 alignment: int | str = "reference"):
         self.path = Path(path)
         self.batch_size = batch_size
         self.device = device
         self.dtype = dtype
         self.nibble_order = nibble_order
+        self.alignment = alignment
         self._reader: Optional[GGUFReader] = None
 
     def open(self):
-        self._reader = GGUFReader(self.path, nibble_order=self.nibble_order)
+        self._reader = GGUFReader(self.path, nibble_order=self.nibble_order, alignment=self.alignment)
         self._reader.__enter__()
 
     def close(self):
@@ -590,8 +612,9 @@ class StreamingDequantizer:
 @contextmanager
 def streaming_dequant_context(path: str | Path, batch_size: int = 4, device: str = "cuda",
                               dtype: torch.dtype = torch.float16, *,
-                              nibble_order: str = "reference") -> Iterator[StreamingDequantizer]:
-    streamer = StreamingDequantizer(path, batch_size, device, dtype, nibble_order=nibble_order)
+                              nibble_order: str = "reference",
+                              alignment: int | str = "reference") -> Iterator[StreamingDequantizer]:
+    streamer = StreamingDequantizer(path, batch_size, device, dtype, nibble_order=nibble_order, alignment=alignment)
     streamer.open()
     try:
         yield streamer
@@ -606,10 +629,11 @@ class GGUFModelPatcher:
     """Writes GGUF tensors into the parameters of a torch module."""
 
     def __init__(self, gguf_path: str | Path, name_mapping: Optional[Dict[str, str]] = None, *,
-                 nibble_order: str = "reference"):
+                 nibble_order: str = "reference", alignment: int | str = "reference"):
         self.gguf_path = Path(gguf_path)
         self.name_mapping = name_mapping or {}
         self.nibble_order = nibble_order
+        self.alignment = alignment
         self._reader: Optional[GGUFReader] = None
 
     def _map_name(self, gguf_name: str) -> str:
@@ -643,7 +667,7 @@ class GGUFModelPatcher:
         stats: Dict[str, Any] = {"loaded": 0, "skipped": 0, "missing": [], "unexpected": []}
         params = dict(model.named_parameters())
         gathers = []
-        with GGUFReader(self.gguf_path, nibble_order=self.nibble_order) as reader:
+        with GGUFReader(self.gguf_path, nibble_order=self.nibble_order, alignment=self.alignment) as reader:
             self._reader = reader
             for gguf_name, info in reader.tensors.items():
                 torch_name = self._map_name(gguf_name)

@@ -56,7 +56,8 @@ def map_tensor_name(gguf_name: str) -> Optional[str]:
 
 
 def load_model_weights(model: torch.nn.Module, path, device: str = "cuda", dtype: torch.dtype = torch.float16,
-                       shard: Optional[Tuple[int, int]] = None, nibble_order: str = "reference") -> Dict[str, int]:
+                       shard: Optional[Tuple[int, int]] = None, nibble_order: str = "reference",
+                       alignment: int | str = "reference") -> Dict[str, int]:
     """Fills ``model`` from the GGUF file at ``path`` and returns ``{"loaded", "skipped"}``.
 
     The module is moved to ``device``/``dtype`` first (what the reference does last), then every
@@ -65,13 +66,13 @@ def load_model_weights(model: torch.nn.Module, path, device: str = "cuda", dtype
     ``shard=(rank, world_size)`` loads row shards into parameters that hold ``rows // world_size`` rows.
     """
     model.to(device=device, dtype=dtype)
-    with GGUFReader(path) as reader:
+    with GGUFReader(path, alignment=alignment) as reader:
         mapping = {name: map_tensor_name(name) for name in reader.tensors}
     usable = {g: p for g, p in mapping.items() if p is not None}
     unmapped = len(mapping) - len(usable)
     # names with no mapping must not fall through to the patcher's own default rule
     patcher = GGUFModelPatcher(path, {**{g: f"\0unmapped.{g}" for g in mapping if g not in usable}, **usable},
-                               nibble_order=nibble_order)
+                               nibble_order=nibble_order, alignment=alignment)
     with patcher.patch_context(model, device=device, dtype=dtype, shard=shard) as stats:
         pass
     logger.info(f"Loaded {stats['loaded']} tensors, skipped {stats['skipped']}")

@@ -132,11 +132,12 @@ class TensorSpec:
         return packed_nbytes(self.ggml_type, self.numel)
 
 
-def _align(n: int) -> int:
-    return (n + ALIGNMENT - 1) // ALIGNMENT * ALIGNMENT
+def _align(n: int, alignment: int = ALIGNMENT) -> int:
+    return (n + alignment - 1) // alignment * alignment
 
 
-def header_bytes(specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str, Any]], version: int = 3) -> Tuple[bytes, List[int]]:
+def header_bytes(specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str, Any]], version: int = 3,
+                 alignment: int = ALIGNMENT) -> Tuple[bytes, List[int]]:
     """Header + key/values + tensor infos, and each tensor's offset in the data section."""
     out = [struct.pack("<IIQQ", GGUF_MAGIC, version, len(specs), len(metadata))]
     for key, kind, value in metadata:
@@ -150,18 +151,21 @@ def header_bytes(specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str,
         out.append(struct.pack("<I", len(dims)))
         out.append(struct.pack(f"<{len(dims)}Q", *dims))
         out.append(struct.pack("<IQ", sp.ggml_type, cur))
-        cur = _align(cur + sp.nbytes)
+        cur = _align(cur + sp.nbytes, alignment)
     return b"".join(out), offsets
 
 
 def write_gguf(path, specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, str, Any]] = (),
                seed: int = 0, contents: Optional[Dict[str, np.ndarray]] = None, version: int = 3,
-               chunk_elems: int = 1 << 26) -> int:
+               chunk_elems: int = 1 << 26, alignment: int = ALIGNMENT) -> int:
     """Writes a GGUF file; returns its size.  Tensors not in ``contents`` get
     seeded random blocks, generated in chunks so that multi-gigabyte tensors
-    never sit in memory whole."""
-    head, offsets = header_bytes(specs, metadata, version)
-    data_start = _align(len(head))
+    never sit in memory whole.  An ``alignment`` other than 32 is recorded as
+    the ``general.alignment`` key and used for the data section and every tensor."""
+    if alignment != ALIGNMENT:
+        metadata = list(metadata) + [("general.alignment", "u32", alignment)]
+    head, offsets = header_bytes(specs, metadata, version, alignment)
+    data_start = _align(len(head), alignment)
     with open(path, "wb") as f:
         f.write(head)
         f.write(b"\0" * (data_start - len(head)))
@@ -177,7 +181,7 @@ def write_gguf(path, specs: Sequence[TensorSpec], metadata: Sequence[Tuple[str, 
                 step = max(chunk_elems // per_block * per_block, per_block)
                 for e0 in range(0, sp.numel, step):
                     f.write(random_packed(sp.ggml_type, min(step, sp.numel - e0), rng).tobytes())
-            pad = _align(f.tell() - data_start) - (f.tell() - data_start)
+            pad = _align(f.tell() - data_start, alignment) - (f.tell() - data_start)
             if pad and i + 1 < len(specs):
                 f.write(b"\0" * pad)
         return f.tell()

@@ -209,3 +209,34 @@ def test_large_string_arrays_native_scan(tmp_path, golden_dir):
     assert list(offs) == [8, 18, 26] and list(lens) == [2, 0, 3]
     assert L.pfhe_scan_string_array(blob, len(blob) - 1, 3, offs, lens) == _native.ERR_SHORT_SOURCE
     assert L.pfhe_scan_string_array(blob, len(blob), 4, offs, lens) == _native.ERR_SHORT_SOURCE
+
+
+def test_general_alignment_opt_in(tmp_path):
+    """The reference rounds the data section to 32 bytes whatever the file says (:321-323); reading
+    ``general.alignment`` is opt-in and changes where the data section (and so every tensor) starts."""
+    specs = [synth.TensorSpec("a", (3, 32), gl.GGML_TYPE_Q8_0), synth.TensorSpec("b", (5,), gl.GGML_TYPE_F32),
+             synth.TensorSpec("c", (2, 32), gl.GGML_TYPE_Q4_0)]
+    rng = np.random.default_rng(5)
+    contents = {sp.name: synth.random_packed(sp.ggml_type, sp.numel, rng) for sp in specs}
+    for align in (8, 64, 256):
+        path = tmp_path / f"aligned{align}.gguf"
+        synth.write_gguf(path, specs, [("general.name", "str", "x" * 3)], contents=contents, alignment=align)
+        with gl.GGUFReader(path, alignment="metadata") as r:
+            assert r.metadata["general.alignment"] == align
+            assert r.header.tensor_data_offset % align == 0
+            for sp in specs:
+                assert r.tensors[sp.name].offset % align == 0
+                assert r.read_tensor_raw(sp.name) == contents[sp.name].tobytes()
+        with gl.GGUFReader(path, alignment=align) as r:
+            assert r.read_tensor_raw("c") == contents["c"].tobytes()
+        with gl.GGUFReader(path) as r:                      # the reference's fixed 32
+            end = r.header.tensor_data_offset
+            assert end % 32 == 0
+    # a file without the key reads the same either way
+    path = tmp_path / "plain.gguf"
+    synth.write_gguf(path, specs, contents=contents)
+    with gl.GGUFReader(path, alignment="metadata") as r:
+        assert r.read_tensor_raw("a") == contents["a"].tobytes()
+    for bad in ("ggml", 0, -32, True, 1.5):
+        with pytest.raises(ValueError):
+            gl.GGUFReader(path, alignment=bad)

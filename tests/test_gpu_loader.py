@@ -318,6 +318,31 @@ def test_nibble_order_option(small_llama):
         gl.GGUFReader(path, nibble_order="other")
 
 
+@pytest.mark.parametrize("align", [8, 64, 4096])
+def test_general_alignment_opt_in(tmp_path, align):
+    """A file laid out on its own ``general.alignment`` decodes through every entry with
+    alignment="metadata"; 8-byte alignment puts block data off the 16-byte lines."""
+    path = tmp_path / "al.gguf"
+    specs = [synth.TensorSpec("a.weight", (33, 96), gl.GGML_TYPE_Q4_0), synth.TensorSpec("b.weight", (7, 64), gl.GGML_TYPE_Q8_0),
+             synth.TensorSpec("c.weight", (9, 32), gl.GGML_TYPE_Q4_1), synth.TensorSpec("n.weight", (37,), gl.GGML_TYPE_F32),
+             synth.TensorSpec("h.weight", (5, 3), gl.GGML_TYPE_F16)]
+    rng = np.random.default_rng(align)
+    contents = {sp.name: synth.random_packed(sp.ggml_type, sp.numel, rng) for sp in specs}
+    synth.write_gguf(path, specs, [("general.name", "str", "odd")], contents=contents, alignment=align)
+    want = {sp.name: np_oracle.read_tensor(sp.ggml_type, contents[sp.name], sp.numel, "bf16").reshape(sp.shape) for sp in specs}
+    with pfhe_b200.tensor_loading_context(path, alignment="metadata") as r:
+        for sp in specs:
+            assert_same_bits(to_bits(r.read_tensor(sp.name, device="cuda", dtype=torch.bfloat16)), want[sp.name], "bf16", sp.name)
+    with pfhe_b200.streaming_dequant_context(path, batch_size=2, dtype=torch.bfloat16, alignment="metadata") as s:
+        for batch in s.iter_batches():
+            for n, t in batch.items():
+                assert_same_bits(to_bits(t), want[n], "bf16", n)
+    lin = torch.nn.Linear(96, 33, bias=False, device="cuda", dtype=torch.bfloat16)
+    with pfhe_b200.GGUFModelPatcher(path, {"a.weight": "weight"}, alignment=align).patch_context(lin, dtype=torch.bfloat16) as stats:
+        assert stats["loaded"] == 1
+    assert_same_bits(to_bits(lin.weight.data), want["a.weight"], "bf16")
+
+
 def test_k_quant_file_through_the_api(tmp_path):
     """A file with the type mix of a llama.cpp Q4_K_M export goes through read_tensor, streaming and
     patch_context; rows shard on whole 256-element blocks; the no-alloc entry point decodes them too."""

@@ -1,7 +1,8 @@
 """Keep-quantised residency: the fused decode-and-multiply kernel against an fp32 torch reference.
 
-Floating-point kernel: weights are bit-exact (checked elsewhere), products are exact in fp32, only the
-order of the fp32 additions differs, so the tolerance is a few ulps of the sum of |terms|:
+Floating-point kernel: Q4_0 / Q8_0 weights are bit-exact (checked elsewhere), Q4_1 weights are q*d + m rounded
+once to fp16 (one fp16 ulp from the decode kernels' double rounding in about 1 of 10^4 weights), products are
+exact in fp32 and only the order of the fp32 additions differs, so the tolerance is a few ulps of the sum of |terms|:
 |y - y_ref| <= 2e-5 * (|x| @ |W|.T) + one fp16 rounding of the result when the output is fp16."""
 import numpy as np
 import pytest
