@@ -124,9 +124,9 @@ typedef struct pfhe_launch_cfg {
     int32_t threads;      /* threads per CTA (multiple of 32) */
     int32_t ctas_per_sm;  /* 0 (default): one tile per CTA, grid = tile count; > 0: persistent grid of SM count * ctas_per_sm */
     int32_t streaming_stores; /* 1: evict-first stores; 0: default; -1: library default */
-    int32_t reserved[2];  /* [0] (persistent grid): 0/2 = tiles dealt round-robin to the CTAs, 1 = one contiguous run per CTA;
-                             [1] (persistent grid): 0 = tile_blocks is a target, adjusted so the tiles fill whole rounds of the grid,
-                                  1 = use tile_blocks exactly */
+    int32_t contiguous_runs; /* persistent grid only: 0 = tiles dealt round-robin to the CTAs, 1 = one contiguous run per CTA */
+    int32_t exact_tile;      /* persistent grid only: 0 = tile_blocks is a target, adjusted so the tiles fill whole rounds
+                                of the grid; 1 = use tile_blocks exactly */
 } pfhe_launch_cfg;
 
 int pfhe_dequant_launch_ex(int ggml_type, int mid_dtype, int out_dtype,

@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
 class LaunchCfg(ctypes.Structure):
     _fields_ = [("variant", ctypes.c_int32), ("tile_blocks", ctypes.c_int32), ("stages", ctypes.c_int32),
                 ("threads", ctypes.c_int32), ("ctas_per_sm", ctypes.c_int32), ("streaming_stores", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 2)]
+                ("contiguous_runs", ctypes.c_int32), ("exact_tile", ctypes.c_int32)]
 
 
 class TensorDesc(ctypes.Structure):

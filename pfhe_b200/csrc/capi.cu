@@ -374,7 +374,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
     fill_packed(&a.t, src8, dst, n, bb, be);
     a.tile_blocks = cfg.tile_blocks;
     a.stages = cfg.stages;
-    a.interleaved = cfg.reserved[0] == 1 ? 0 : 1;
+    a.interleaved = cfg.contiguous_runs == 1 ? 0 : 1;
     if ((rc = status_word(dev, &a.status))) return rc;
 
     // Small tensors: fewer CTAs, so every CTA has at least one 8-block group.
@@ -386,7 +386,7 @@ int launch_decode(int ggml_type, int mid, int out, const void *src, int64_t src_
         grid = (n_blocks + a.tile_blocks - 1) / a.tile_blocks;
         a.stages = 1;
         a.interleaved = 1;
-    } else if (cfg.reserved[1] == 0) {
+    } else if (cfg.exact_tile == 0) {
         // Tiles near the requested length that fill whole rounds of the grid.
         const size_t per_cta = kSmemBudget / (size_t)(cfg.ctas_per_sm > 0 ? cfg.ctas_per_sm : 1) - 1024;
         int max_tile = (int)(per_cta / ((size_t)a.stages * bb) - 16) / 8 * 8;
