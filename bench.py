@@ -488,6 +488,35 @@ def run_model_loads(args, rank, world, dev, torch, dist):
             }
             del model
             torch.cuda.empty_cache()
+            if args.replicated_load and world > 1:
+                try:
+                    # replicated layout: every rank ends with the whole model; it decodes its own rows and the
+                    # rest arrives by NCCL all-gather, enqueued per tensor beside the staging of the next ones
+                    full = _module_tree(torch, {sp.name: tuple(sp.shape) for sp in specs}, torch.bfloat16, dev)
+                    full_bytes = sum(p.numel() * 2 for p in full.parameters())
+                    rtimes = []
+                    for _ in range(2):
+                        gl.wait_for_deferred_unmaps()
+                        barrier()
+                        t0 = time.perf_counter()
+                        with pfhe_b200.GGUFModelPatcher(path).patch_context(full, device=str(dev), dtype=torch.bfloat16,
+                                                                           shard=(rank, world),
+                                                                           replicate_group=dist.group.WORLD) as stats:
+                            pass
+                        torch.cuda.synchronize()
+                        t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                        rtimes.append(float(t[0]))
+                        assert stats["loaded"] == len(specs) and not stats["missing"], stats
+                    out["llama3_70b_q4_1_to_bf16_replicated"] = {
+                        "api": "patch_context(dtype=bfloat16, shard=(rank, world), replicate_group=WORLD)", "n_gpus": world,
+                        "load_seconds": min(rtimes), "load_seconds_each": rtimes, "decoded_gb_per_gpu": full_bytes / 1e9,
+                        "gathered_gb_per_gpu": full_bytes * (world - 1) / world / 1e9,
+                    }
+                    del full
+                    torch.cuda.empty_cache()
+                except Exception as e:
+                    out["llama3_70b_q4_1_to_bf16_replicated"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     except Exception as e:                       # keep the headline line even if this leg cannot run
         out["llama3_70b_q4_1_to_bf16"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     finally:
@@ -730,6 +759,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=16, help="tensors per step")
     ap.add_argument("--traffic-bytes", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture (profiles/), echoed into the roofline object")
+    ap.add_argument("--replicated-load", action="store_true",
+                    help="with --gpus N > 1: also time the 70B-shaped load into a replicated (full-size) model per GPU")
     ap.add_argument("--no-model-load", action="store_true",
                     help="skip the whole-model load legs (7B-shaped streaming, 70B-shaped sharded patch)")
     ap.add_argument("--kernel-case", default=None,

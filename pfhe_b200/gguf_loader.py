@@ -660,9 +660,11 @@ class GGUFModelPatcher:
             replicated.
         replicate_group: a ``torch.distributed`` process group.  With ``shard``,
             parameters that hold the full shape are filled by decoding only this
-            rank's rows and all-gathering the rest over the group (NCCL).
+            rank's rows and all-gathering the rest over the group (NCCL).  Each
+            gather is enqueued as soon as its tensor's decode is and runs beside the
+            staging and decode of the tensors that follow.
         """
-        from .sharding import row_range
+        from .sharding import all_gather_rows, row_range
 
         stats: Dict[str, Any] = {"loaded": 0, "skipped": 0, "missing": [], "unexpected": []}
         params = dict(model.named_parameters())
@@ -706,13 +708,11 @@ class GGUFModelPatcher:
                         else:
                             param.copy_(tensor)
                     if gather:
-                        gathers.append(param.data)
+                        gathers.extend(all_gather_rows(param.data, replicate_group, async_op=True))
                 stats["loaded"] += 1
 
-            if gathers:
-                from .sharding import all_gather_rows
-                for full in gathers:
-                    all_gather_rows(full, replicate_group)
+            for work in gathers:
+                work.wait()
 
             mapped = {self._map_name(n) for n in reader.tensors}
             stats["missing"] = [n for n in params if n not in mapped]

@@ -55,12 +55,16 @@ def plan_bytes(tensors: Iterable[GGUFTensorInfo], rank: int, world_size: int) ->
     return b, e
 
 
-def all_gather_rows(full: torch.Tensor, group=None) -> None:
+def all_gather_rows(full: torch.Tensor, group=None, async_op: bool = False) -> list:
     """Completes a replicated tensor in place.
 
     Every rank has already written its own ``row_range`` slice of ``full``;
     afterwards every rank holds all rows.  Equal shares use one
-    ``all_gather_into_tensor``; ragged shares fall back to per-rank broadcasts.
+    ``all_gather_into_tensor`` (on CUDA the rank's own slice is the send buffer:
+    NCCL's in-place form, no staging copy); ragged shares fall back to per-rank
+    broadcasts.  With ``async_op`` the collectives are only enqueued (behind the
+    work already on the current stream) and their handles are returned; the
+    caller waits on them before the tensor is used.
     """
     import torch.distributed as dist
 
@@ -68,13 +72,16 @@ def all_gather_rows(full: torch.Tensor, group=None) -> None:
     rank = dist.get_rank(group)
     rows = full.shape[0]
     if world == 1:
-        return
+        return []
+    works = []
     if rows % world == 0:
         r0, r1 = row_range(rows, rank, world)
-        mine = full[r0:r1].clone()          # the input may not alias the output
-        dist.all_gather_into_tensor(full, mine, group=group)
-        return
-    for src in range(world):
-        r0, r1 = row_range(rows, src, world)
-        if r1 > r0:
-            dist.broadcast(full[r0:r1], src=dist.get_global_rank(group, src) if group is not None else src, group=group)
+        mine = full[r0:r1] if full.is_cuda else full[r0:r1].clone()
+        works.append(dist.all_gather_into_tensor(full, mine, group=group, async_op=async_op))
+    else:
+        for src in range(world):
+            r0, r1 = row_range(rows, src, world)
+            if r1 > r0:
+                works.append(dist.broadcast(full[r0:r1], src=dist.get_global_rank(group, src) if group is not None else src,
+                                            group=group, async_op=async_op))
+    return [w for w in works if w is not None] if async_op else []

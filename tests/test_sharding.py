@@ -96,8 +96,14 @@ def _gather_worker(rank, world, port, rows, cols, q):
         sub = dist.new_group(list(range(world)))
         full2 = torch.zeros(rows, cols, dtype=torch.bfloat16)
         full2[r0:r1] = whole[r0:r1]
-        sh.all_gather_rows(full2, sub)
-        q.put((rank, bool(torch.equal(full, whole)) and bool(torch.equal(full2, whole))))
+        assert sh.all_gather_rows(full2, sub) == []
+        full3 = torch.zeros(rows, cols, dtype=torch.bfloat16)   # enqueue now, wait later: what patch_context does
+        full3[r0:r1] = whole[r0:r1]
+        works = sh.all_gather_rows(full3, None, async_op=True)
+        assert works
+        for w in works:
+            w.wait()
+        q.put((rank, bool(torch.equal(full, whole)) and bool(torch.equal(full2, whole)) and bool(torch.equal(full3, whole))))
     finally:
         dist.destroy_process_group()
 
