@@ -32,7 +32,7 @@ def _reference(t, raw, rows, cols, x):
 
 
 @pytest.mark.parametrize("fmt", list(TYPES))
-@pytest.mark.parametrize("rows,cols", [(16, 256), (4096, 4096), (1000, 1024), (11008, 4096), (33, 8192), (4096, 11008 // 256 * 256)])
+@pytest.mark.parametrize("rows,cols", [(5, 512), (16, 256), (4096, 4096), (1000, 1024), (11008, 4096), (33, 8192), (4096, 11008 // 256 * 256)])
 @pytest.mark.parametrize("batch", [1, 3, 8])
 def test_fused_gemv_matches_fp32_reference(fmt, rows, cols, batch):
     t, raw, x = _case(fmt, rows, cols, batch, rows + cols + batch)
@@ -47,6 +47,21 @@ def test_fused_gemv_matches_fp32_reference(fmt, rows, cols, batch):
     y16 = quantized_matmul(x, raw, (rows, cols), t)
     assert y16.dtype == torch.float16 and tuple(y16.shape) == (batch, rows)
     assert bool(((y16.float() - ref).abs() <= 2e-5 * bound + ref.abs() * 2 ** -10 + 1e-7).all())
+
+
+@pytest.mark.parametrize("fmt", ["Q4_0", "Q4_1", "Q8_0"])
+def test_fused_gemv_many_rows(fmt):
+    """From 65,536 rows up the 4-bit kernels put two row tiles in a CTA; a row count that is not a
+    multiple of 32 leaves the last CTA with one tile and a ragged one."""
+    rows, cols, batch = 65536 + 40, 512, 5
+    t, raw, x = _case(fmt, rows, cols, batch, 99)
+    ref, bound = _reference(t, raw, rows, cols, x)
+    y = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    _native.check(_native.lib().pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols,
+                                                   y.data_ptr(), _native.OUT_F32, rows, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _native.check(_native.lib().pfhe_device_status(-1))
+    assert bool(((y - ref).abs() <= 2e-5 * bound + 1e-30).all())
 
 
 def test_ggml_order_weights_and_wrappers():
