@@ -210,7 +210,7 @@ int pfhe_device_status(int device);
 
 /*
  * Decode-time product on packed weights: y[m][n] = sum_k x[m][k] * W[n][k] for
- * batch m = 1..8, W of shape (rows, cols) kept in its GGUF block format (Q4_0,
+ * batch m = 1..32, W of shape (rows, cols) kept in its GGUF block format (Q4_0,
  * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER) and decoded on the
  * fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
  * (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight

@@ -1,5 +1,5 @@
 // Decode-time matrix product on packed weights: Y[m][n] = sum_k X[m][k] * W[n][k] for a small
-// batch m <= 8, with W kept in its GGUF block format and decoded on the fly.  Takes over
+// batch m <= 32, with W kept in its GGUF block format and decoded on the fly.  Takes over
 // quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
 // (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight to fp16 in HBM
 // first and then call F.linear; here the packed bytes are read once (0.56 / 0.63 / 1.06 bytes per
@@ -185,7 +185,7 @@ struct GemvArgs {
     void *y;                // [batch][ldy] outputs, fp32 or fp16
     int64_t rows;
     int32_t k_blocks;       // K / 32 (a multiple of kGemvChunkBlocks)
-    int32_t batch;          // 1..8
+    int32_t batch;          // 1..32
     int64_t ldx, ldy;
     int32_t pitch;          // bytes between the staged segments of consecutive rows
     int32_t y_is_f16;
@@ -204,7 +204,9 @@ inline int padded_pitch(int seg_bytes)
     return p;
 }
 
-template <int T>
+// NT: batch tiles of eight activation rows (1, 2 or 4).  The decoded weights of a block pair are
+// used for every batch tile, so 32 rows cost about 1.9 times the instructions of 8, not 4 times.
+template <int T, int NT>
 __global__ void __launch_bounds__(kGemvWarps * 32) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
 {
     using F = GemvFmt<T>;
@@ -212,7 +214,6 @@ __global__ void __launch_bounds__(kGemvWarps * 32) quant_gemv_kernel(const __gri
     constexpr int CB = kGemvChunkBlocks;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_all[kGemvWarps * kGemvStages];
-    __shared__ float red[kGemvWarps][32][4];
 
     // the warp index as a value the compiler knows to be the same in all lanes, so that the copy
     // addresses below are computed once per warp and not once per lane
@@ -256,10 +257,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) quant_gemv_kernel(const __gri
     };
     for (int i = 0; i < n_mine && i < kGemvStages; ++i) issue(i);
 
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};     // even / odd blocks: two independent chains
+    float acc[NT][2][4];                    // per batch tile: even / odd blocks, two independent chains
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[j][e >> 2][e & 3] = 0.f;
     // Lanes whose batch column does not exist read column 0: a column of B only reaches the same
     // column of the accumulators, which is never stored for them.
-    const __half *xrow = a.x + (int64_t)(g < a.batch ? g : 0) * a.ldx;
+    const __half *xrow[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) xrow[j] = a.x + (int64_t)(8 * j + g < a.batch ? 8 * j + g : 0) * a.ldx;
     uint32_t parity_bits = 0;
     bool failed = false;
     for (int i = 0; i < n_mine; ++i) {
@@ -273,22 +280,25 @@ __global__ void __launch_bounds__(kGemvWarps * 32) quant_gemv_kernel(const __gri
         const int b0 = c * CB;
         const uint32_t *rowA = reinterpret_cast<const uint32_t *>(ring + (size_t)s * stage_bytes + (size_t)g * pitch);
         const uint32_t *rowB = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(rowA) + 8 * pitch);
-        const __half *xb = xrow + (int64_t)b0 * 32;
         auto pair = [&](int p) {                                // blocks 2p and 2p+1: a pair starts on a 4-byte boundary
             const uint32_t *WA = rowA + p * F::kPairWords;
             const uint32_t *WB = rowB + p * F::kPairWords;
-            uint32_t xe[4], xo[4];
-            x_frags<T>(xb + p * 64, t, xe);
-            x_frags<T>(xb + p * 64 + 32, t, xo);
-            uint32_t ra[4], rb[4];
-            block_frags<T, 0>(WA, t, magic, ra);
-            block_frags<T, 0>(WB, t, magic, rb);
-            mma_m16n8k16(acc0, ra[0], rb[0], ra[1], rb[1], xe[0], xe[1]);
-            mma_m16n8k16(acc0, ra[2], rb[2], ra[3], rb[3], xe[2], xe[3]);
-            block_frags<T, 1>(WA, t, magic, ra);
-            block_frags<T, 1>(WB, t, magic, rb);
-            mma_m16n8k16(acc1, ra[0], rb[0], ra[1], rb[1], xo[0], xo[1]);
-            mma_m16n8k16(acc1, ra[2], rb[2], ra[3], rb[3], xo[2], xo[3]);
+            uint32_t ea[4], eb[4], oa[4], ob[4];
+            block_frags<T, 0>(WA, t, magic, ea);
+            block_frags<T, 0>(WB, t, magic, eb);
+            block_frags<T, 1>(WA, t, magic, oa);
+            block_frags<T, 1>(WB, t, magic, ob);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const __half *xb = xrow[j] + (int64_t)b0 * 32 + p * 64;
+                uint32_t xe[4], xo[4];
+                x_frags<T>(xb, t, xe);
+                x_frags<T>(xb + 32, t, xo);
+                mma_m16n8k16(acc[j][0], ea[0], eb[0], ea[1], eb[1], xe[0], xe[1]);
+                mma_m16n8k16(acc[j][0], ea[2], eb[2], ea[3], eb[3], xe[2], xe[3]);
+                mma_m16n8k16(acc[j][1], oa[0], ob[0], oa[1], ob[1], xo[0], xo[1]);
+                mma_m16n8k16(acc[j][1], oa[2], ob[2], oa[3], ob[3], xo[2], xo[3]);
+            }
         };
 #pragma unroll
         for (int p = 0; p < CB / 2; ++p) pair(p);
@@ -301,23 +311,32 @@ __global__ void __launch_bounds__(kGemvWarps * 32) quant_gemv_kernel(const __gri
             (void)mbar_wait_bounded(&full[s], (parity_bits >> s) & 1u, kDeviceWaitLimitNs / 8);
     }
 
-    // cross-warp reduction of each 16 x 8 tile over its k_splits warps, then one store per (row, batch column)
+    // Cross-warp reduction of each 16 x 8 tile over its k_splits warps, then one store per (row,
+    // batch column).  A warp parks its partial sums in its own ring, which it no longer needs.
+    float *park = reinterpret_cast<float *>(ring);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) red[warp][lane][j] = acc0[j] + acc1[j];
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) park[(j * 4 + e) * 32 + lane] = acc[j][0][e] + acc[j][1][e];
     __syncthreads();
     if (ksplit == 0) {                      // warps 0 .. row_tiles-1, one per row tile
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int w = tile; w < kGemvWarps; w += row_tiles) {
-            sum[0] += red[w][lane][0]; sum[1] += red[w][lane][1]; sum[2] += red[w][lane][2]; sum[3] += red[w][lane][3];
-        }
-        // c0: (row g, col 2t)  c1: (row g, col 2t+1)  c2: (row g+8, col 2t)  c3: (row g+8, col 2t+1); col = batch index
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t r = row0 + g + (j >> 1) * 8;
-            const int m = 2 * t + (j & 1);
-            if (r < a.rows && m < a.batch) {
-                if (a.y_is_f16) reinterpret_cast<__half *>(a.y)[(int64_t)m * a.ldy + r] = __float2half_rn(sum[j]);
-                else reinterpret_cast<float *>(a.y)[(int64_t)m * a.ldy + r] = sum[j];
+        for (int j = 0; j < NT; ++j) {
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int w = tile; w < kGemvWarps; w += row_tiles) {
+                const float *from = reinterpret_cast<const float *>(smem + (size_t)w * kGemvStages * stage_bytes);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sum[e] += from[(j * 4 + e) * 32 + lane];
+            }
+            // c0: (row g, col 2t)  c1: (row g, col 2t+1)  c2: (row g+8, col 2t)  c3: (row g+8, col 2t+1); col = batch index
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int64_t r = row0 + g + (e >> 1) * 8;
+                const int m = 8 * j + 2 * t + (e & 1);
+                if (r < a.rows && m < a.batch) {
+                    if (a.y_is_f16) reinterpret_cast<__half *>(a.y)[(int64_t)m * a.ldy + r] = __float2half_rn(sum[e]);
+                    else reinterpret_cast<float *>(a.y)[(int64_t)m * a.ldy + r] = sum[e];
+                }
             }
         }
     }
@@ -389,10 +408,14 @@ int make_weight_map(const GemvArgs &a, int block_bytes, CUtensorMap *map)
     return PFHE_OK;
 }
 
-template <int T> int launch_gemv(const GemvArgs &a, cudaStream_t stream)
+template <int T, int NT = 1> int launch_gemv(const GemvArgs &a, cudaStream_t stream)
 {
+    if constexpr (NT == 1) {
+        if (a.batch > 16) return launch_gemv<T, 4>(a, stream);
+        if (a.batch > 8) return launch_gemv<T, 2>(a, stream);
+    }
     const size_t smem = (size_t)kGemvWarps * kGemvStages * 16 * a.pitch;
-    auto fn = quant_gemv_kernel<T>;
+    auto fn = quant_gemv_kernel<T, NT>;
     static std::atomic<unsigned long long> configured{0};          // bit per device
     int dev = 0;
     if (current_device(&dev)) return PFHE_ERR_CUDA;
@@ -428,8 +451,8 @@ extern "C" int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_b
         return PFHE_ERR_BAD_TYPE;
     }
     if (y_dtype != O_F32 && y_dtype != O_F16) { set_error("output dtype must be f32 or f16"); return PFHE_ERR_BAD_DTYPE; }
-    if (rows < 0 || cols < 0 || batch < 1 || batch > 8 || ldx < cols || ldy < rows) {
-        set_error("bad shape: rows %lld cols %lld batch %d (1..8) ldx %lld ldy %lld", (long long)rows, (long long)cols, batch,
+    if (rows < 0 || cols < 0 || batch < 1 || batch > 32 || ldx < cols || ldy < rows) {
+        set_error("bad shape: rows %lld cols %lld batch %d (1..32) ldx %lld ldy %lld", (long long)rows, (long long)cols, batch,
                   (long long)ldx, (long long)ldy);
         return PFHE_ERR_BAD_ARG;
     }

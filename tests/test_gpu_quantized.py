@@ -96,10 +96,28 @@ def test_large_batch_and_odd_shapes_fall_back_to_decode_then_linear():
     ref, bound = _reference(t, raw, rows, cols, x)
     y = quantized_matmul(x, raw, (rows, cols), t)
     assert bool(((y.float() - ref).abs() <= 1e-3 * bound + 1e-3).all())
-    t, raw, x = _case("Q8_0", 256, 1024, 20, 9)          # batch > 8
+    t, raw, x = _case("Q8_0", 256, 1024, 40, 9)          # more than 32 rows of activations
     ref, bound = _reference(t, raw, 256, 1024, x)
     y = quantized_matmul(x, raw, (256, 1024), t)
-    assert tuple(y.shape) == (20, 256) and bool(((y.float() - ref).abs() <= 1e-3 * bound + 1e-3).all())
+    assert tuple(y.shape) == (40, 256) and bool(((y.float() - ref).abs() <= 1e-3 * bound + 1e-3).all())
+
+
+@pytest.mark.parametrize("fmt", list(TYPES))
+@pytest.mark.parametrize("batch", [9, 20, 32])
+def test_nine_to_thirty_two_rows_take_the_fused_kernel(fmt, batch):
+    rows, cols = 520, 2048
+    t, raw, x = _case(fmt, rows, cols, batch, 31 + batch)
+    ref, bound = _reference(t, raw, rows, cols, x)
+    before = _native.lib().pfhe_launch_count()
+    y = quantized_matmul(x, raw, (rows, cols), t)
+    if not (fmt == "Q8_0" and batch > 16):                      # Q8_0 hands 17+ rows to decode-then-multiply
+        assert _native.lib().pfhe_launch_count() - before == 1  # one fused launch, no decode launch
+    y32 = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    _native.check(_native.lib().pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y32.data_ptr(),
+                                                   _native.OUT_F32, rows, torch.cuda.current_stream().cuda_stream))
+    assert bool(((y32 - ref).abs() <= 2e-5 * bound + 1e-30).all())
+    assert tuple(y.shape) == (batch, rows)
+    assert bool(((y.float() - ref).abs() <= 2e-5 * bound + ref.abs() * 2 ** -10 + 1e-7).all())
 
 
 def test_gemv_argument_errors():
@@ -111,7 +129,7 @@ def test_gemv_argument_errors():
                                                                                   256, y.data_ptr(), ydt, 16, None)
     assert call(12, 16, 256, 1) == _native.ERR_BAD_TYPE                 # a K-quant
     assert call(2, 16, 128, 1) == _native.ERR_BAD_ARG                   # cols not a multiple of 256
-    assert call(2, 16, 256, 9) == _native.ERR_BAD_ARG                   # batch > 8
+    assert call(2, 16, 256, 33) == _native.ERR_BAD_ARG                  # batch > 32
     assert call(2, 16, 256, 1, wbytes=100) == _native.ERR_SHORT_SOURCE
     assert call(2, 16, 256, 1, ydt=2) == _native.ERR_BAD_DTYPE          # bf16 output is not offered
     assert call(2, 0, 256, 1) == _native.OK
