@@ -207,7 +207,7 @@ inline int padded_pitch(int seg_bytes)
 // NT: batch tiles of eight activation rows (1, 2 or 4).  The decoded weights of a block pair are
 // used for every batch tile, so 32 rows cost about 1.9 times the instructions of 8, not 4 times.
 template <int T, int NT>
-__global__ void __launch_bounds__(kGemvWarps * 32) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
+__global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? 5 : (NT == 2 ? 3 : 2)) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
 {
     using F = GemvFmt<T>;
     constexpr int BB = F::kBB;
