@@ -229,6 +229,23 @@ int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_bytes, int64
                         void *y_dev, int y_dtype, int64_t ldy, void *stream);
 
 /*
+ * The same product with a caller-provided device workspace (no counterpart in
+ * the reference).  A small kernel first rewrites x into the order in which the
+ * multiply kernel's warps consume it (pfhe_quantized_gemv_workspace_bytes(cols,
+ * batch) bytes, 16-byte aligned), so that each warp fetches its activations
+ * with one coalesced load instead of a gather over up to eight rows of x and
+ * four byte permutes.  Results are bit-identical to pfhe_quantized_gemv.  Worth
+ * it from two rows of activations up, or for very large weights; with
+ * workspace_dev == NULL this is pfhe_quantized_gemv.  The workspace is free
+ * again once the work queued on `stream` has run.
+ */
+int64_t pfhe_quantized_gemv_workspace_bytes(int64_t cols, int batch);
+int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t w_bytes, int64_t rows, int64_t cols,
+                           const void *x_dev, int batch, int64_t ldx,
+                           void *y_dev, int y_dtype, int64_t ldy,
+                           void *workspace_dev, int64_t workspace_bytes, void *stream);
+
+/*
  * Self-test of the failure path (no counterpart in the reference): launches a
  * one-warp kernel that waits, with the same bounded wait the decode kernels
  * use, on a barrier that nothing completes.  After limit_ms (1..1000) the

@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "pfhe_version", "pfhe_last_error_string", "pfhe_tensor_nbytes", "pfhe_scan_string_array",
     "pfhe_dequant_launch", "pfhe_dequant_launch_cast2", "pfhe_dequant_launch_ex", "pfhe_dequant_launch_batch", "pfhe_dequant_launch_batch_ex",
     "pfhe_dequant_from_host_noalloc", "pfhe_device_status", "pfhe_launch_count", "pfhe_selftest_bounded_wait", "pfhe_quantized_gemv",
+    "pfhe_quantized_gemv_ws", "pfhe_quantized_gemv_workspace_bytes",
     "pfhe_loader_create", "pfhe_loader_submit", "pfhe_loader_submit_fd", "pfhe_loader_upload",
     "pfhe_loader_wait", "pfhe_loader_get_stats", "pfhe_loader_destroy",
 )
@@ -88,6 +89,10 @@ def lib() -> ctypes.CDLL:
     L.pfhe_selftest_bounded_wait.argtypes = [i32, ctypes.POINTER(i64), vp]
     L.pfhe_quantized_gemv.restype = i32
     L.pfhe_quantized_gemv.argtypes = [i32, vp, i64, i64, i64, vp, i32, i64, vp, i32, i64, vp]
+    L.pfhe_quantized_gemv_ws.restype = i32
+    L.pfhe_quantized_gemv_ws.argtypes = [i32, vp, i64, i64, i64, vp, i32, i64, vp, i32, i64, vp, i64, vp]
+    L.pfhe_quantized_gemv_workspace_bytes.restype = i64
+    L.pfhe_quantized_gemv_workspace_bytes.argtypes = [i64, i32]
     L.pfhe_launch_count.restype = i64
     L.pfhe_loader_create.restype = i32
     L.pfhe_loader_create.argtypes = [i32, i32, i64, i32, ctypes.POINTER(vp)]

@@ -179,9 +179,48 @@ template <int T> __device__ __forceinline__ void x_frags(const __half *xb, int t
     }
 }
 
+// Element of the 32-element block that k slot `slot` (0..7) of quad thread t holds, in the order
+// block_frags produces its registers (two slots per register, registers 0..3).
+template <int T> __device__ __forceinline__ int slot_element(int t, int slot)
+{
+    using F = GemvFmt<T>;
+    const int reg = slot >> 1, hi = slot & 1;
+    if constexpr (F::kFour && !F::kGgml) return 8 * t + reg + 4 * hi;                      // (0,4) (1,5) (2,6) (3,7)
+    else if constexpr (F::kFour) return 4 * t + 16 * (reg & 1) + (reg >> 1) + 2 * hi;      // (0,2) (16,18) (1,3) (17,19)
+    else return 4 * t + 16 * (reg >> 1) + 2 * (reg & 1) + hi;                              // (0,1) (2,3) (16,17) (18,19)
+}
+
+// Activations rewritten in the order the multiply kernel consumes them: for block b, batch tile j
+// and lane l the eight halves of that lane's B registers, 16 bytes, at ((b * tiles + j) * 32 + l).
+// One warp-wide 16-byte load then fetches what would otherwise be a gather over eight rows of x
+// followed by four byte-permutes.  Rows past `batch` are written as zeros.
+template <int T>
+__global__ void pack_activations_kernel(const __half *x, int64_t ldx, int batch, int tiles, int k_blocks, uint4 *packed)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t total = (int64_t)k_blocks * tiles * 32;
+    if (idx >= total) return;
+    const int lane = (int)(idx & 31);
+    const int j = (int)((idx >> 5) % tiles);
+    const int64_t b = (idx >> 5) / tiles;
+    const int g = lane >> 2, t = lane & 3;
+    const int m = 8 * j + g;
+    uint32_t r[4] = {0u, 0u, 0u, 0u};
+    if (m < batch) {
+        const unsigned short *row = reinterpret_cast<const unsigned short *>(x + (int64_t)m * ldx + b * 32);
+#pragma unroll
+        for (int slot = 0; slot < 8; ++slot) {
+            const uint32_t h = __ldg(row + slot_element<T>(t, slot));
+            r[slot >> 1] |= h << (16 * (slot & 1));
+        }
+    }
+    packed[idx] = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 struct GemvArgs {
     const uint8_t *w;       // packed weights, 16-byte aligned, rows of (K/32)*block_bytes bytes
     const __half *x;        // [batch][ldx] activations
+    const uint4 *xp;        // activations in fragment order (pack_activations_kernel), or null
     void *y;                // [batch][ldy] outputs, fp32 or fp16
     int64_t rows;
     int32_t k_blocks;       // K / 32 (a multiple of kGemvChunkBlocks)
@@ -206,7 +245,7 @@ inline int padded_pitch(int seg_bytes)
 
 // NT: batch tiles of eight activation rows (1, 2 or 4).  The decoded weights of a block pair are
 // used for every batch tile, so 32 rows cost about 1.9 times the instructions of 8, not 4 times.
-template <int T, int NT>
+template <int T, int NT, bool kPacked>
 __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? 5 : (NT == 2 ? 3 : 2)) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
 {
     using F = GemvFmt<T>;
@@ -290,10 +329,17 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? 5 : (NT == 2 ? 3 : 
             block_frags<T, 1>(WB, t, magic, ob);
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const __half *xb = xrow[j] + (int64_t)b0 * 32 + p * 64;
                 uint32_t xe[4], xo[4];
-                x_frags<T>(xb, t, xe);
-                x_frags<T>(xb + 32, t, xo);
+                if constexpr (kPacked) {
+                    const uint4 *xq = a.xp + ((int64_t)(b0 + 2 * p) * NT + j) * 32 + lane;
+                    const uint4 ve = __ldg(xq), vo = __ldg(xq + NT * 32);
+                    xe[0] = ve.x; xe[1] = ve.y; xe[2] = ve.z; xe[3] = ve.w;
+                    xo[0] = vo.x; xo[1] = vo.y; xo[2] = vo.z; xo[3] = vo.w;
+                } else {
+                    const __half *xb = xrow[j] + (int64_t)b0 * 32 + p * 64;
+                    x_frags<T>(xb, t, xe);
+                    x_frags<T>(xb + 32, t, xo);
+                }
                 mma_m16n8k16(acc[j][0], ea[0], eb[0], ea[1], eb[1], xe[0], xe[1]);
                 mma_m16n8k16(acc[j][0], ea[2], eb[2], ea[3], eb[3], xe[2], xe[3]);
                 mma_m16n8k16(acc[j][1], oa[0], ob[0], oa[1], ob[1], xo[0], xo[1]);
@@ -408,14 +454,27 @@ int make_weight_map(const GemvArgs &a, int block_bytes, CUtensorMap *map)
     return PFHE_OK;
 }
 
-template <int T, int NT = 1> int launch_gemv(const GemvArgs &a, cudaStream_t stream)
+template <int T, int NT = 1, bool kPacked = false> int launch_gemv(const GemvArgs &a, cudaStream_t stream)
 {
-    if constexpr (NT == 1) {
+    if constexpr (NT == 1 && !kPacked) {
+        if (a.xp) {
+            if (a.batch > 16) return launch_gemv<T, 4, true>(a, stream);
+            if (a.batch > 8) return launch_gemv<T, 2, true>(a, stream);
+            return launch_gemv<T, 1, true>(a, stream);
+        }
         if (a.batch > 16) return launch_gemv<T, 4>(a, stream);
         if (a.batch > 8) return launch_gemv<T, 2>(a, stream);
     }
+    if constexpr (kPacked) {
+        const int64_t total = (int64_t)a.k_blocks * NT * 32;
+        pack_activations_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a.x, a.ldx, a.batch, NT, a.k_blocks,
+                                                                                        const_cast<uint4 *>(a.xp));
+        cudaError_t pe = cudaGetLastError();
+        if (pe != cudaSuccess) return cuda_fail(pe, "activation packing launch");
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    }
     const size_t smem = (size_t)kGemvWarps * kGemvStages * 16 * a.pitch;
-    auto fn = quant_gemv_kernel<T, NT>;
+    auto fn = quant_gemv_kernel<T, NT, kPacked>;
     static std::atomic<unsigned long long> configured{0};          // bit per device
     int dev = 0;
     if (current_device(&dev)) return PFHE_ERR_CUDA;
@@ -437,9 +496,16 @@ template <int T, int NT = 1> int launch_gemv(const GemvArgs &a, cudaStream_t str
 
 }  // namespace
 
-extern "C" int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_bytes, int64_t rows, int64_t cols,
-                                   const void *x_dev, int batch, int64_t ldx, void *y_dev, int y_dtype, int64_t ldy,
-                                   void *stream_)
+extern "C" int64_t pfhe_quantized_gemv_workspace_bytes(int64_t cols, int batch)
+{
+    if (cols < 0 || batch < 1 || batch > 32) return 0;
+    const int tiles = batch > 16 ? 4 : (batch > 8 ? 2 : 1);
+    return (cols / 32) * tiles * 32 * (int64_t)sizeof(uint4);
+}
+
+extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t w_bytes, int64_t rows, int64_t cols,
+                                      const void *x_dev, int batch, int64_t ldx, void *y_dev, int y_dtype, int64_t ldy,
+                                      void *workspace_dev, int64_t workspace_bytes, void *stream_)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     int be = 0, bb = 0;
@@ -465,11 +531,19 @@ extern "C" int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_b
         set_error("weights and activations must be 16-byte aligned (ldx a multiple of 8)");
         return PFHE_ERR_BAD_ARG;
     }
+    if (workspace_dev) {
+        const int64_t want = pfhe_quantized_gemv_workspace_bytes(cols, batch);
+        if (workspace_bytes < want || reinterpret_cast<uintptr_t>(workspace_dev) % 16) {
+            set_error("workspace of %lld bytes (16-byte aligned) needed, got %lld", (long long)want, (long long)workspace_bytes);
+            return PFHE_ERR_BAD_ARG;
+        }
+    }
     int dev = 0;
     if ((rc = current_device(&dev))) return rc;
     GemvArgs a;
     a.w = static_cast<const uint8_t *>(w_dev);
     a.x = static_cast<const __half *>(x_dev);
+    a.xp = static_cast<const uint4 *>(workspace_dev);
     a.y = y_dev;
     a.rows = rows;
     a.k_blocks = (int32_t)(cols / 32);
@@ -492,4 +566,11 @@ extern "C" int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_b
     case T_Q4_1G: return launch_gemv<T_Q4_1G>(a, stream);
     default: return launch_gemv<T_Q8_0>(a, stream);
     }
+}
+
+extern "C" int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_bytes, int64_t rows, int64_t cols,
+                                   const void *x_dev, int batch, int64_t ldx, void *y_dev, int y_dtype, int64_t ldy,
+                                   void *stream)
+{
+    return pfhe_quantized_gemv_ws(ggml_type, w_dev, w_bytes, rows, cols, x_dev, batch, ldx, y_dev, y_dtype, ldy, nullptr, 0, stream);
 }

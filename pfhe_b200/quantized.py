@@ -20,7 +20,9 @@ from .resident import decode_resident
 
 GEMV_TYPES = (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0)
 GEMV_MAX_BATCH = 32         # rows of activations the fused kernel takes in one launch
-GEMV_MAX_BATCH_Q8_0 = 16    # for Q8_0 the decode-then-multiply path catches up at 32 rows (measured)
+# Repacking the activations into the kernel's consumption order costs one small launch (about 4 us)
+# and pays from roughly this many (packed weight bytes x activation rows) up; measured on B200.
+GEMV_PACK_X_THRESHOLD = 800e6
 
 
 class QuantizedTensor:
@@ -71,8 +73,8 @@ def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int,
                      nibble_order: str = "reference") -> torch.Tensor:
     """``x @ W.T`` for packed ``W`` of logical shape ``(out_features, in_features)``; returns fp16.
 
-    ``x`` is ``[..., in_features]``.  At most 32 rows of activations (16 for Q8_0), an in_features that is a
-    multiple of 256 and a Q4_0 / Q4_1 / Q8_0 weight take the fused kernel; everything else decodes then multiplies.
+    ``x`` is ``[..., in_features]``.  At most 32 rows of activations, an in_features that is a multiple of
+    256 and a Q4_0 / Q4_1 / Q8_0 weight take the fused kernel; everything else decodes then multiplies.
     """
     out_features, in_features = w_shape
     lead = x.shape[:-1]
@@ -81,8 +83,7 @@ def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int,
     ktype = quant_type
     if nibble_order == "ggml" and quant_type in (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1):
         ktype |= _native.TYPE_FLAG_GGML_ORDER
-    max_rows = GEMV_MAX_BATCH_Q8_0 if quant_type == GGML_TYPE_Q8_0 else GEMV_MAX_BATCH
-    fused = (quant_type in GEMV_TYPES and 1 <= batch <= max_rows and in_features % 256 == 0
+    fused = (quant_type in GEMV_TYPES and 1 <= batch <= GEMV_MAX_BATCH and in_features % 256 == 0
              and x2.is_cuda and w_quant.is_cuda and w_quant.data_ptr() % 16 == 0)
     if not fused:
         w = decode_resident([(w_quant.contiguous().view(torch.uint8), ktype, (out_features, in_features))], torch.float16)[0]
@@ -91,14 +92,18 @@ def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int,
     if x2.data_ptr() % 16:
         x2 = x2.clone()
     y = torch.empty((batch, out_features), dtype=torch.float16, device=x2.device)
+    w_bytes = w_quant.numel() * w_quant.element_size()
+    pack_x = batch >= 2 and (w_bytes * batch >= GEMV_PACK_X_THRESHOLD or (quant_type == GGML_TYPE_Q8_0 and batch > 16))
     with torch.cuda.device(x2.device):
-        stream = torch.cuda.current_stream(x2.device).cuda_stream
-        for b0 in range(0, batch, GEMV_MAX_BATCH):
-            nb = min(GEMV_MAX_BATCH, batch - b0)
-            _native.check(_native.lib().pfhe_quantized_gemv(
-                ktype, w_quant.data_ptr(), w_quant.numel() * w_quant.element_size(), out_features, in_features,
-                x2.data_ptr() + b0 * in_features * 2, nb, in_features, y.data_ptr() + b0 * out_features * 2, _native.OUT_F16,
-                out_features, stream))
+        L = _native.lib()
+        work, work_bytes = None, 0
+        if pack_x:
+            work_bytes = L.pfhe_quantized_gemv_workspace_bytes(in_features, batch)
+            work = torch.empty(work_bytes, dtype=torch.uint8, device=x2.device)   # caching allocator: stream-ordered reuse
+        _native.check(L.pfhe_quantized_gemv_ws(
+            ktype, w_quant.data_ptr(), w_bytes, out_features, in_features, x2.data_ptr(), batch, in_features,
+            y.data_ptr(), _native.OUT_F16, out_features, work.data_ptr() if work is not None else None, work_bytes,
+            torch.cuda.current_stream(x2.device).cuda_stream))
     return y.reshape(*lead, out_features)
 
 

@@ -64,6 +64,36 @@ def test_fused_gemv_many_rows(fmt):
     assert bool(((y - ref).abs() <= 2e-5 * bound + 1e-30).all())
 
 
+@pytest.mark.parametrize("fmt,flag", [("Q4_0", 0), ("Q4_0", 0x100), ("Q4_1", 0), ("Q4_1", 0x100), ("Q8_0", 0)])
+@pytest.mark.parametrize("batch", [1, 3, 8, 13, 16, 27, 32])
+def test_workspace_entry_is_bit_identical(fmt, flag, batch):
+    """pfhe_quantized_gemv_ws repacks the activations first; same products, same order, same bits."""
+    rows, cols = 300, 1024
+    t, raw, x = _case(fmt, rows, cols, batch, 7 * batch)
+    t |= flag
+    L = _native.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    y0 = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    y1 = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    _native.check(L.pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y0.data_ptr(),
+                                        _native.OUT_F32, rows, st))
+    nbytes = L.pfhe_quantized_gemv_workspace_bytes(cols, batch)
+    assert nbytes == cols // 32 * (1 if batch <= 8 else 2 if batch <= 16 else 4) * 512
+    work = torch.empty(nbytes + 16, dtype=torch.uint8, device="cuda")
+    _native.check(L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y1.data_ptr(),
+                                           _native.OUT_F32, rows, work.data_ptr(), nbytes, st))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    assert torch.equal(y0.view(torch.int32), y1.view(torch.int32))
+    ref, bound = _reference(t, raw, rows, cols, x)
+    assert bool(((y1 - ref).abs() <= 2e-5 * bound + 1e-30).all())
+    # too small or misaligned workspaces are refused
+    assert L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y1.data_ptr(),
+                                    _native.OUT_F32, rows, work.data_ptr(), nbytes - 1, st) == _native.ERR_BAD_ARG
+    assert L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y1.data_ptr(),
+                                    _native.OUT_F32, rows, work.data_ptr() + 8, nbytes, st) == _native.ERR_BAD_ARG
+
+
 def test_ggml_order_weights_and_wrappers():
     rows, cols = 512, 2048
     t, raw, x = _case("Q4_1", rows, cols, 2, 5)
@@ -110,8 +140,8 @@ def test_nine_to_thirty_two_rows_take_the_fused_kernel(fmt, batch):
     ref, bound = _reference(t, raw, rows, cols, x)
     before = _native.lib().pfhe_launch_count()
     y = quantized_matmul(x, raw, (rows, cols), t)
-    if not (fmt == "Q8_0" and batch > 16):                      # Q8_0 hands 17+ rows to decode-then-multiply
-        assert _native.lib().pfhe_launch_count() - before == 1  # one fused launch, no decode launch
+    packs = fmt == "Q8_0" and batch > 16                        # the activation repacking launch
+    assert _native.lib().pfhe_launch_count() - before == (2 if packs else 1)      # no decode launch
     y32 = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
     _native.check(_native.lib().pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y32.data_ptr(),
                                                    _native.OUT_F32, rows, torch.cuda.current_stream().cuda_stream))
