@@ -302,9 +302,12 @@ def run_gpu_arm(args) -> None:
 
     # --- whole-model loads (after the timed legs; needs the HBM the batch buffers hold) ----------
     model_load = None
+    gemv = None
     if not args.no_model_load:
         del srcs, dsts, descs
         torch.cuda.empty_cache()
+        if world == 1:
+            gemv = run_gemv_leg(torch)
         model_load = run_model_loads(args, rank, world, dev, torch, dist)
 
     # --- max over ranks -------------------------------------------------------------------
@@ -354,6 +357,8 @@ def run_gpu_arm(args) -> None:
             line["cpu_baseline"] = cpu_base
         if model_load is not None:
             line["model_load"] = model_load
+        if gemv is not None:
+            line["quantized_gemv"] = gemv
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -363,6 +368,55 @@ def run_gpu_arm(args) -> None:
 # ---------------------------------------------------------------------------------------------
 # Whole-model loads (reported beside the headline metric)
 # ---------------------------------------------------------------------------------------------
+def run_gemv_leg(torch) -> dict:
+    """Keep-quantised residency: the fused decode-and-multiply kernel on an FFN-sized (28672 x 8192) weight, packed
+    weight bytes per second, beside the reference's formulation (decode the whole weight to fp16, then F.linear)."""
+    from pfhe_b200 import _native
+    from pfhe_b200.resident import decode_resident
+    L = _native.lib()
+    rows, cols = 28672, 8192
+    st = torch.cuda.current_stream().cuda_stream
+    out = {"weight": f"{rows}x{cols}", "unit": "GB/s of packed weight bytes", "timing": "40 launches over 4 rotated weights, CUDA events, best of 3"}
+    for name, t in (("Q4_0", 2), ("Q8_0", 8)):
+        nb = L.pfhe_tensor_nbytes(t, rows * cols)
+        ws = [torch.randint(0, 255, (nb,), dtype=torch.uint8, device="cuda") for _ in range(4)]
+        for batch in (1, 8):
+            x = torch.randn(batch, cols, device="cuda").half()
+            y = torch.empty(batch, rows, dtype=torch.float16, device="cuda")
+            nws = L.pfhe_quantized_gemv_workspace_bytes(cols, batch)
+            work = torch.empty(nws, dtype=torch.uint8, device="cuda")
+
+            def fused(i):
+                _native.check(L.pfhe_quantized_gemv_ws(t, ws[i % 4].data_ptr(), nb, rows, cols, x.data_ptr(), batch, cols, y.data_ptr(),
+                                                       _native.OUT_F16, rows, work.data_ptr() if batch > 1 else None, nws, st))
+
+            def decode_then_linear(i):
+                w = decode_resident([(ws[i % 4], t, (rows, cols))], torch.float16)[0]
+                return torch.nn.functional.linear(x, w)
+
+            res = {}
+            for label, fn, n in (("fused", fused, 40), ("decode_then_linear", decode_then_linear, 12)):
+                for i in range(4):
+                    fn(i)
+                torch.cuda.synchronize()
+                best = float("inf")
+                for _ in range(3):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for i in range(n):
+                        fn(i)
+                    b.record()
+                    torch.cuda.synchronize()
+                    best = min(best, a.elapsed_time(b) / n)
+                res[label + "_us"] = best * 1e3
+            res["fused_gbps"] = nb / res["fused_us"] / 1e3
+            out[f"{name}_batch{batch}"] = res
+        del ws
+        torch.cuda.empty_cache()
+    _native.check(L.pfhe_device_status(-1))
+    return out
+
+
 def _module_tree(torch, shapes, dtype, device):
     """A bare module whose named_parameters() are exactly the dotted GGUF names."""
     root = torch.nn.Module()
