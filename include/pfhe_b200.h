@@ -211,8 +211,8 @@ int pfhe_device_status(int device);
 /*
  * Decode-time product on packed weights: y[m][n] = sum_k x[m][k] * W[n][k] for
  * batch m = 1..32, W of shape (rows, cols) kept in its GGUF block format (Q4_0,
- * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER) and decoded on the
- * fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
+ * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER, or Q4_K) and decoded
+ * on the fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
  * (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight
  * to fp16 in device memory and then call F.linear.  Every Q4_0 / Q8_0 weight
  * takes exactly the fp16 value pfhe_dequant_launch(..., PFHE_OUT_F16) gives it;
@@ -220,6 +220,10 @@ int pfhe_device_status(int device);
  * fp32 first, one fp16 ulp apart in rare double-rounding cases).  x is fp16,
  * products and sums are fp32; the result differs from an fp32 reference on the
  * decoded weights by summation order (and, for Q4_1, by those rare ulps).
+ * Q4_K multiplies with the unrounded fp32 weights (d*sc)*q - dmin*m of the
+ * decode kernels' fp32 output (scales applied once per 32-element sub-block
+ * after the tensor-core sum), i.e. without the fp16 rounding of each weight
+ * that decode-to-fp16-then-multiply has.
  * cols must be a multiple of 256; w_dev and x_dev 16-byte
  * aligned; x is [batch][ldx] halves, y is [batch][ldy] of y_dtype (PFHE_OUT_F32
  * or PFHE_OUT_F16).

@@ -82,7 +82,8 @@ template <int T> struct GemvFmt {
     static constexpr int kBase = T & ~T_ORDER_FLAG;
     static constexpr bool kGgml = (T & T_ORDER_FLAG) != 0;
     static constexpr bool kFour = kBase == T_Q4_0 || kBase == T_Q4_1;
-    static constexpr int kBB = Fmt<T>::kBytes;
+    static constexpr bool kSuper = kBase == T_Q4_K;          // 256-element super-block with 6-bit sub-block scales
+    static constexpr int kBB = Fmt<T>::kBytes * 32 / Fmt<T>::kElems;   // bytes per 32 elements (18 for Q4_K: 144 / 8)
     static constexpr int kPairWords = 2 * kBB / 4;          // 9, 10, 17 aligned words per pair of blocks
 };
 
@@ -166,7 +167,13 @@ template <int T> __device__ __forceinline__ void x_frags(const __half *xb, int t
     } else {
         const uint2 lo = __ldg(reinterpret_cast<const uint2 *>(xb + 4 * t));        // elements 4t .. 4t+3
         const uint2 hi = __ldg(reinterpret_cast<const uint2 *>(xb + 16 + 4 * t));   // elements 16+4t .. 16+4t+3
-        if constexpr (F::kFour) {
+        if constexpr (F::kSuper) {
+            // one byte per element, bytes 0 and 2 of a word extracted together: (4t, 4t+2) (4t+1, 4t+3), then 16 + the same
+            b[0] = __byte_perm(lo.x, lo.y, 0x5410);
+            b[1] = __byte_perm(lo.x, lo.y, 0x7632);
+            b[2] = __byte_perm(hi.x, hi.y, 0x5410);
+            b[3] = __byte_perm(hi.x, hi.y, 0x7632);
+        } else if constexpr (F::kFour) {
             // byte 4t+j: low nibble = element 4t+j, high nibble = element 16+4t+j, so the nibble pairs are
             // (4t, 4t+2) (16+4t, 16+4t+2) (4t+1, 4t+3) (16+4t+1, 16+4t+3)
             b[0] = __byte_perm(lo.x, lo.y, 0x5410);
@@ -179,13 +186,56 @@ template <int T> __device__ __forceinline__ void x_frags(const __half *xb, int t
     }
 }
 
+// ---- Q4_K: 144-byte super-blocks of 256 elements (fp16 d, fp16 dmin, 12 bytes of 6-bit scales and
+// minimums, 128 nibble bytes); y = (d * sc) * q - (dmin * m) per 32-element sub-block, as ggml's
+// dequantize_row_q4_K.  The kernel feeds the tensor cores 64 + q (exact in fp16, no subtract and
+// no per-weight multiply), gets sum_k x_k of the sub-block from a second instruction whose A
+// operand is all ones, and applies the two fp32 coefficients once per sub-block and output:
+//   acc += (d*sc) * sum((64 + q) x) - (64 * (d*sc) + dmin*m) * sum(x).
+// The weights are therefore the unrounded fp32 values, not their fp16 roundings.
+struct K4Scales { uint32_t sc_lo, sc_hi, m_lo, m_hi; float d, dmin; };
+__device__ __forceinline__ K4Scales k4_scales(const uint32_t *W)          // W: the aligned words of one super-block
+{
+    const uint32_t w0 = W[0], w1 = W[1], w2 = W[2], w3 = W[3];
+    K4Scales s;
+    s.sc_lo = w1 & 0x3F3F3F3Fu;                                            // sub-blocks 0..3, one byte each
+    s.m_lo = w2 & 0x3F3F3F3Fu;
+    s.sc_hi = (w3 & 0x0F0F0F0Fu) | ((w1 >> 2) & 0x30303030u);             // sub-blocks 4..7
+    s.m_hi = ((w3 >> 4) & 0x0F0F0F0Fu) | ((w2 >> 2) & 0x30303030u);
+    s.d = half_bits_to_f32(w0 & 0xFFFFu);
+    s.dmin = half_bits_to_f32(w0 >> 16);
+    return s;
+}
+__device__ __forceinline__ float byte_as_float(uint32_t x, int i)         // i is a constant after unrolling
+{
+    return __fsub_rn(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540 + i)), 8388608.0f);
+}
+// (d * sc, 64 * d * sc + dmin * m) of sub-block S; both products are exact in fp32.
+__device__ __forceinline__ void k4_coefficients(const K4Scales &s, int S, float &mul, float &off)
+{
+    const float sc = byte_as_float(S < 4 ? s.sc_lo : s.sc_hi, S & 3);
+    const float mn = byte_as_float(S < 4 ? s.m_lo : s.m_hi, S & 3);
+    mul = __fmul_rn(s.d, sc);
+    off = __fmaf_rn(64.0f, mul, __fmul_rn(s.dmin, mn));
+}
+// From one word of four nibble bytes: lo[0..1] = 64 + low nibbles of bytes (0,2), (1,3);
+// hi[0..1] = 64 + high nibbles of the same bytes.
+__device__ __forceinline__ void k4_nibbles(uint32_t w, uint32_t magic64, uint32_t (&lo)[2], uint32_t (&hi)[2])
+{
+    lo[0] = and_or(w << 4, 0x00F000F0u, magic64);
+    lo[1] = and_or(w >> 4, 0x00F000F0u, magic64);
+    hi[0] = and_or(w, 0x00F000F0u, magic64);
+    hi[1] = and_or(w >> 8, 0x00F000F0u, magic64);
+}
+
 // Element of the 32-element block that k slot `slot` (0..7) of quad thread t holds, in the order
 // block_frags produces its registers (two slots per register, registers 0..3).
 template <int T> __device__ __forceinline__ int slot_element(int t, int slot)
 {
     using F = GemvFmt<T>;
     const int reg = slot >> 1, hi = slot & 1;
-    if constexpr (F::kFour && !F::kGgml) return 8 * t + reg + 4 * hi;                      // (0,4) (1,5) (2,6) (3,7)
+    if constexpr (F::kSuper) return 4 * t + 16 * (reg >> 1) + (reg & 1) + 2 * hi;          // (0,2) (1,3) (16,18) (17,19)
+    else if constexpr (F::kFour && !F::kGgml) return 8 * t + reg + 4 * hi;                 // (0,4) (1,5) (2,6) (3,7)
     else if constexpr (F::kFour) return 4 * t + 16 * (reg & 1) + (reg >> 1) + 2 * hi;      // (0,2) (16,18) (1,3) (17,19)
     else return 4 * t + 16 * (reg >> 1) + 2 * (reg & 1) + hi;                              // (0,1) (2,3) (16,17) (18,19)
 }
@@ -246,7 +296,7 @@ inline int padded_pitch(int seg_bytes)
 // NT: batch tiles of eight activation rows (1, 2 or 4).  The decoded weights of a block pair are
 // used for every batch tile, so 32 rows cost about 1.9 times the instructions of 8, not 4 times.
 template <int T, int NT, bool kPacked>
-__global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? 5 : (NT == 2 ? 3 : 2)) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
+__global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper ? 4 : 5) : (NT == 2 ? 3 : 2)) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
 {
     using F = GemvFmt<T>;
     constexpr int BB = F::kBB;
@@ -320,6 +370,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? 5 : (NT == 2 ? 3 : 
         const uint32_t *rowA = reinterpret_cast<const uint32_t *>(ring + (size_t)s * stage_bytes + (size_t)g * pitch);
         const uint32_t *rowB = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(rowA) + 8 * pitch);
         auto pair = [&](int p) {                                // blocks 2p and 2p+1: a pair starts on a 4-byte boundary
+            if constexpr (F::kSuper) return;
             const uint32_t *WA = rowA + p * F::kPairWords;
             const uint32_t *WB = rowB + p * F::kPairWords;
             uint32_t ea[4], eb[4], oa[4], ob[4];
@@ -346,8 +397,52 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? 5 : (NT == 2 ? 3 : 
                 mma_m16n8k16(acc[j][1], oa[2], ob[2], oa[3], ob[3], xo[2], xo[3]);
             }
         };
+        // Q4_K: the chunk is one super-block per row; sub-blocks 2J (low nibbles) and 2J+1 (high
+        // nibbles) share the 32 bytes at qs + 32 J, of which this thread takes words t and t + 4.
+        auto super_pair = [&](int J, const K4Scales &sa, const K4Scales &sb) {
+            const uint32_t *qa = rowA + 4 + 8 * J, *qb = rowB + 4 + 8 * J;
+            uint32_t al0[2], ah0[2], al1[2], ah1[2], bl0[2], bh0[2], bl1[2], bh1[2];
+            k4_nibbles(qa[t], magic.hi, al0, ah0);
+            k4_nibbles(qa[t + 4], magic.hi, al1, ah1);
+            k4_nibbles(qb[t], magic.hi, bl0, bh0);
+            k4_nibbles(qb[t + 4], magic.hi, bl1, bh1);
 #pragma unroll
-        for (int p = 0; p < CB / 2; ++p) pair(p);
+            for (int h = 0; h < 2; ++h) {
+                float mul_a, off_a, mul_b, off_b;
+                k4_coefficients(sa, 2 * J + h, mul_a, off_a);
+                k4_coefficients(sb, 2 * J + h, mul_b, off_b);
+                const uint32_t (&a0)[2] = h ? ah0 : al0, (&a1)[2] = h ? ah1 : al1;
+                const uint32_t (&c0)[2] = h ? bh0 : bl0, (&c1)[2] = h ? bh1 : bl1;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    uint32_t xs[4];
+                    if constexpr (kPacked) {
+                        const uint4 v = __ldg(a.xp + ((int64_t)(b0 + 2 * J + h) * NT + j) * 32 + lane);
+                        xs[0] = v.x; xs[1] = v.y; xs[2] = v.z; xs[3] = v.w;
+                    } else {
+                        x_frags<T>(xrow[j] + (int64_t)(b0 + 2 * J + h) * 32, t, xs);
+                    }
+                    float dot[4] = {0.f, 0.f, 0.f, 0.f}, sum[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_m16n8k16(dot, a0[0], c0[0], a0[1], c0[1], xs[0], xs[1]);
+                    mma_m16n8k16(dot, a1[0], c1[0], a1[1], c1[1], xs[2], xs[3]);
+                    constexpr uint32_t kOnes = 0x3C003C00u;         // every row of A is ones: every row of `sum` is sum_k x_k
+                    mma_m16n8k16(sum, kOnes, kOnes, kOnes, kOnes, xs[0], xs[1]);
+                    mma_m16n8k16(sum, kOnes, kOnes, kOnes, kOnes, xs[2], xs[3]);
+                    acc[j][0][0] = __fmaf_rn(-off_a, sum[0], __fmaf_rn(mul_a, dot[0], acc[j][0][0]));
+                    acc[j][0][1] = __fmaf_rn(-off_a, sum[1], __fmaf_rn(mul_a, dot[1], acc[j][0][1]));
+                    acc[j][0][2] = __fmaf_rn(-off_b, sum[2], __fmaf_rn(mul_b, dot[2], acc[j][0][2]));
+                    acc[j][0][3] = __fmaf_rn(-off_b, sum[3], __fmaf_rn(mul_b, dot[3], acc[j][0][3]));
+                }
+            }
+        };
+        if constexpr (F::kSuper) {
+            const K4Scales sa = k4_scales(rowA), sb = k4_scales(rowB);
+#pragma unroll
+            for (int J = 0; J < 4; ++J) super_pair(J, sa, sb);
+        } else {
+#pragma unroll
+            for (int p = 0; p < CB / 2; ++p) pair(p);
+        }
         __syncwarp();
         if (i + kGemvStages < n_mine) issue(i + kGemvStages);
     }
@@ -484,7 +579,7 @@ template <int T, int NT = 1, bool kPacked = false> int launch_gemv(const GemvArg
         configured.fetch_or(1ull << dev);
     }
     CUtensorMap wmap;
-    int rc = make_weight_map(a, Fmt<T>::kBytes, &wmap);
+    int rc = make_weight_map(a, GemvFmt<T>::kBB, &wmap);
     if (rc) return rc;
     const int64_t grid = (a.rows + 16 * a.row_tiles - 1) / (16 * a.row_tiles);
     fn<<<(unsigned)grid, kGemvWarps * 32, smem, stream>>>(wmap, a);
@@ -512,8 +607,8 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     int rc = type_geometry(ggml_type, &be, &bb);
     if (rc) return rc;
     const int base = ggml_type & ~T_ORDER_FLAG;
-    if (base != T_Q4_0 && base != T_Q4_1 && base != T_Q8_0) {
-        set_error("pfhe_quantized_gemv handles Q4_0, Q4_1 and Q8_0 weights, not ggml type %d", ggml_type);
+    if (base != T_Q4_0 && base != T_Q4_1 && base != T_Q8_0 && ggml_type != T_Q4_K) {
+        set_error("pfhe_quantized_gemv handles Q4_0, Q4_1, Q8_0 and Q4_K weights, not ggml type %d", ggml_type);
         return PFHE_ERR_BAD_TYPE;
     }
     if (y_dtype != O_F32 && y_dtype != O_F16) { set_error("output dtype must be f32 or f16"); return PFHE_ERR_BAD_DTYPE; }
@@ -523,7 +618,7 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
         return PFHE_ERR_BAD_ARG;
     }
     if (cols % 256) { set_error("cols must be a multiple of 256 (rows of whole 8-block groups), got %lld", (long long)cols); return PFHE_ERR_BAD_ARG; }
-    const int64_t need = rows * (cols / 32) * bb;
+    const int64_t need = rows * (cols / be) * bb;
     if (w_bytes < need) { set_error("Data too short: %lld < %lld", (long long)w_bytes, (long long)need); return PFHE_ERR_SHORT_SOURCE; }
     if (rows == 0 || cols == 0) return PFHE_OK;
     if (!w_dev || !x_dev || !y_dev) { set_error("null device pointer"); return PFHE_ERR_BAD_ARG; }
@@ -550,7 +645,7 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     a.batch = batch;
     a.ldx = ldx;
     a.ldy = ldy;
-    a.pitch = padded_pitch(kGemvChunkBlocks * bb);
+    a.pitch = padded_pitch(kGemvChunkBlocks * (bb * 32 / be));
     // Two row tiles per CTA let pairs of warps share their activation reads through L1: measured
     // 3-13 % faster for the 4-bit formats from 128256 x 8192 up, slower for Q8_0 and for small matrices.
     a.row_tiles = (base != T_Q8_0 && rows >= 65536) ? 2 : 1;
@@ -564,6 +659,7 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     case T_Q4_1: return launch_gemv<T_Q4_1>(a, stream);
     case T_Q4_0G: return launch_gemv<T_Q4_0G>(a, stream);
     case T_Q4_1G: return launch_gemv<T_Q4_1G>(a, stream);
+    case T_Q4_K: return launch_gemv<T_Q4_K>(a, stream);
     default: return launch_gemv<T_Q8_0>(a, stream);
     }
 }

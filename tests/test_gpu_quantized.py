@@ -94,6 +94,40 @@ def test_workspace_entry_is_bit_identical(fmt, flag, batch):
                                     _native.OUT_F32, rows, work.data_ptr() + 8, nbytes, st) == _native.ERR_BAD_ARG
 
 
+@pytest.mark.parametrize("rows,cols", [(5, 512), (16, 256), (1000, 1024), (4096, 4096), (33, 8192)])
+@pytest.mark.parametrize("batch", [1, 3, 8, 13, 32])
+@pytest.mark.parametrize("workspace", [False, True])
+def test_q4_k_fused_gemv(rows, cols, batch, workspace):
+    """Q4_K multiplies with the unrounded fp32 weights (d*sc)*q - dmin*m of ggml's decode, so the reference is the
+    fp32 decode; the kernel forms (d*sc)*sum((64+q)x) - (64*d*sc + dmin*m)*sum(x) per sub-block, whose two terms
+    are up to ~20 times the size of their difference: tolerance 4e-5 of sum|w x| plus 2e-6 of max|w| * sum|x|."""
+    t = 12
+    raw = torch.from_numpy(synth.random_packed(t, rows * cols, np.random.default_rng(rows + batch))).cuda()
+    g = torch.Generator(device="cuda").manual_seed(batch)
+    x = torch.randn(batch, cols, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+    w32 = decode_resident([(raw, t, (rows, cols))], torch.float32)[0].double()
+    xd = x.double()
+    ref, bound = xd @ w32.T, xd.abs() @ w32.abs().T
+    slack = 2e-6 * w32.abs().max() * xd.abs().sum(dim=1, keepdim=True)
+    L = _native.lib()
+    y = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    nws = L.pfhe_quantized_gemv_workspace_bytes(cols, batch)
+    work = torch.empty(nws, dtype=torch.uint8, device="cuda")
+    _native.check(L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y.data_ptr(),
+                                           _native.OUT_F32, rows, work.data_ptr() if workspace else None, nws,
+                                           torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    err = (y.double() - ref).abs()
+    assert bool((err <= 4e-5 * bound + slack).all()), float((err / (4e-5 * bound + slack)).max())
+    # through the Python mirror: fp16 output, and against decode-to-fp16-then-multiply within the fp16 rounding of each weight
+    y16 = quantized_matmul(x, raw, (rows, cols), t)
+    assert y16.dtype == torch.float16
+    assert bool(((y16.double() - ref).abs() <= 4e-5 * bound + slack + ref.abs() * 2 ** -10 + 1e-7).all())
+    w16 = decode_resident([(raw, t, (rows, cols))], torch.float16)[0].double()
+    assert bool(((y.double() - xd @ w16.T).abs() <= 2 ** -11 * bound + 4e-5 * bound + slack).all())
+
+
 def test_ggml_order_weights_and_wrappers():
     rows, cols = 512, 2048
     t, raw, x = _case("Q4_1", rows, cols, 2, 5)
@@ -157,7 +191,7 @@ def test_gemv_argument_errors():
     y = torch.zeros(8, 16, dtype=torch.float32, device="cuda")
     call = lambda t, rows, cols, batch, wbytes=4096, ydt=0: L.pfhe_quantized_gemv(t, buf.data_ptr(), wbytes, rows, cols, x.data_ptr(), batch,
                                                                                   256, y.data_ptr(), ydt, 16, None)
-    assert call(12, 16, 256, 1) == _native.ERR_BAD_TYPE                 # a K-quant
+    assert call(14, 16, 256, 1) == _native.ERR_BAD_TYPE                 # Q6_K has no fused kernel
     assert call(2, 16, 128, 1) == _native.ERR_BAD_ARG                   # cols not a multiple of 256
     assert call(2, 16, 256, 33) == _native.ERR_BAD_ARG                  # batch > 32
     assert call(2, 16, 256, 1, wbytes=100) == _native.ERR_SHORT_SOURCE
