@@ -671,7 +671,7 @@ def run_gemv_case(parts) -> None:
     """GEMV:FORMAT:ROWS:COLS:BATCH[:LAUNCHES] -- a few launches of pfhe_quantized_gemv (for profilers)."""
     import torch
     from pfhe_b200 import _native
-    fmt = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8}[parts[1]]
+    fmt = {"Q4_0": 2, "Q4_1": 3, "Q8_0": 8, "Q4_K": 12}[parts[1]]
     rows, cols, batch = int(parts[2]), int(parts[3]), int(parts[4])
     launches = int(parts[5]) if len(parts) > 5 else 6
     L = _native.lib()
