@@ -238,7 +238,10 @@ int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_bytes, int64
  * multiply kernel's warps consume it (pfhe_quantized_gemv_workspace_bytes(cols,
  * batch) bytes, 16-byte aligned), so that each warp fetches its activations
  * with one coalesced load instead of a gather over up to eight rows of x and
- * four byte permutes.  Results are bit-identical to pfhe_quantized_gemv.  Worth
+ * four byte permutes.  Results are bit-identical to pfhe_quantized_gemv for
+ * Q4_0, Q4_1 and Q8_0; for Q4_K the pass also sums each block's activations
+ * (the kernel otherwise gets those sums from the tensor cores), so results
+ * agree up to the fp32 order of that sum.  Worth
  * it from two rows of activations up, or for very large weights; with
  * workspace_dev == NULL this is pfhe_quantized_gemv.  The workspace is free
  * again once the work queued on `stream` has run.

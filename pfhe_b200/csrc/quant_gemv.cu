@@ -245,10 +245,10 @@ template <int T> __device__ __forceinline__ int slot_element(int t, int slot)
 // One warp-wide 16-byte load then fetches what would otherwise be a gather over eight rows of x
 // followed by four byte-permutes.  Rows past `batch` are written as zeros.
 template <int T>
-__global__ void pack_activations_kernel(const __half *x, int64_t ldx, int batch, int tiles, int k_blocks, uint4 *packed)
+__global__ void pack_activations_kernel(const __half *x, int64_t ldx, int batch, int tiles, int k_blocks, uint4 *packed, float *sums)
 {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t total = (int64_t)k_blocks * tiles * 32;
+    const int64_t total = (int64_t)k_blocks * tiles * 32;     // a multiple of 32: warps leave here whole
     if (idx >= total) return;
     const int lane = (int)(idx & 31);
     const int j = (int)((idx >> 5) % tiles);
@@ -256,21 +256,29 @@ __global__ void pack_activations_kernel(const __half *x, int64_t ldx, int batch,
     const int g = lane >> 2, t = lane & 3;
     const int m = 8 * j + g;
     uint32_t r[4] = {0u, 0u, 0u, 0u};
+    float s = 0.f;
     if (m < batch) {
         const unsigned short *row = reinterpret_cast<const unsigned short *>(x + (int64_t)m * ldx + b * 32);
 #pragma unroll
         for (int slot = 0; slot < 8; ++slot) {
             const uint32_t h = __ldg(row + slot_element<T>(t, slot));
             r[slot >> 1] |= h << (16 * (slot & 1));
+            s += half_bits_to_f32(h);
         }
     }
     packed[idx] = make_uint4(r[0], r[1], r[2], r[3]);
+    // sum of the block's 32 activations per batch column (the four lanes of a quad hold eight each):
+    // what the Q4_K kernel multiplies its per-sub-block offsets with
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (t == 0) sums[(idx >> 5) * 8 + g] = s;
 }
 
 struct GemvArgs {
     const uint8_t *w;       // packed weights, 16-byte aligned, rows of (K/32)*block_bytes bytes
     const __half *x;        // [batch][ldx] activations
     const uint4 *xp;        // activations in fragment order (pack_activations_kernel), or null
+    const float *xsum;      // with xp: sum of each block's 32 activations per batch column, [block][tile][8]
     void *y;                // [batch][ldy] outputs, fp32 or fp16
     int64_t rows;
     int32_t k_blocks;       // K / 32 (a multiple of kGemvChunkBlocks)
@@ -425,9 +433,15 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
                     float dot[4] = {0.f, 0.f, 0.f, 0.f}, sum[4] = {0.f, 0.f, 0.f, 0.f};
                     mma_m16n8k16(dot, a0[0], c0[0], a0[1], c0[1], xs[0], xs[1]);
                     mma_m16n8k16(dot, a1[0], c1[0], a1[1], c1[1], xs[2], xs[3]);
-                    constexpr uint32_t kOnes = 0x3C003C00u;         // every row of A is ones: every row of `sum` is sum_k x_k
-                    mma_m16n8k16(sum, kOnes, kOnes, kOnes, kOnes, xs[0], xs[1]);
-                    mma_m16n8k16(sum, kOnes, kOnes, kOnes, kOnes, xs[2], xs[3]);
+                    if constexpr (kPacked) {                        // the repacking pass has already summed the block
+                        const float2 sx = __ldg(reinterpret_cast<const float2 *>(a.xsum + ((int64_t)(b0 + 2 * J + h) * NT + j) * 8 + 2 * t));
+                        sum[0] = sum[2] = sx.x;
+                        sum[1] = sum[3] = sx.y;
+                    } else {
+                        constexpr uint32_t kOnes = 0x3C003C00u;     // every row of A is ones: every row of `sum` is sum_k x_k
+                        mma_m16n8k16(sum, kOnes, kOnes, kOnes, kOnes, xs[0], xs[1]);
+                        mma_m16n8k16(sum, kOnes, kOnes, kOnes, kOnes, xs[2], xs[3]);
+                    }
                     acc[j][0][0] = __fmaf_rn(-off_a, sum[0], __fmaf_rn(mul_a, dot[0], acc[j][0][0]));
                     acc[j][0][1] = __fmaf_rn(-off_a, sum[1], __fmaf_rn(mul_a, dot[1], acc[j][0][1]));
                     acc[j][0][2] = __fmaf_rn(-off_b, sum[2], __fmaf_rn(mul_b, dot[2], acc[j][0][2]));
@@ -563,7 +577,8 @@ template <int T, int NT = 1, bool kPacked = false> int launch_gemv(const GemvArg
     if constexpr (kPacked) {
         const int64_t total = (int64_t)a.k_blocks * NT * 32;
         pack_activations_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(a.x, a.ldx, a.batch, NT, a.k_blocks,
-                                                                                        const_cast<uint4 *>(a.xp));
+                                                                                        const_cast<uint4 *>(a.xp),
+                                                                                        const_cast<float *>(a.xsum));
         cudaError_t pe = cudaGetLastError();
         if (pe != cudaSuccess) return cuda_fail(pe, "activation packing launch");
         g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -595,7 +610,7 @@ extern "C" int64_t pfhe_quantized_gemv_workspace_bytes(int64_t cols, int batch)
 {
     if (cols < 0 || batch < 1 || batch > 32) return 0;
     const int tiles = batch > 16 ? 4 : (batch > 8 ? 2 : 1);
-    return (cols / 32) * tiles * 32 * (int64_t)sizeof(uint4);
+    return (cols / 32) * tiles * (32 * (int64_t)sizeof(uint4) + 8 * (int64_t)sizeof(float));
 }
 
 extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t w_bytes, int64_t rows, int64_t cols,
@@ -639,6 +654,11 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     a.w = static_cast<const uint8_t *>(w_dev);
     a.x = static_cast<const __half *>(x_dev);
     a.xp = static_cast<const uint4 *>(workspace_dev);
+    a.xsum = nullptr;
+    if (workspace_dev) {
+        const int tiles = batch > 16 ? 4 : (batch > 8 ? 2 : 1);
+        a.xsum = reinterpret_cast<const float *>(static_cast<const uint8_t *>(workspace_dev) + (cols / 32) * tiles * 32 * (int64_t)sizeof(uint4));
+    }
     a.y = y_dev;
     a.rows = rows;
     a.k_blocks = (int32_t)(cols / 32);

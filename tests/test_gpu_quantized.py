@@ -67,7 +67,8 @@ def test_fused_gemv_many_rows(fmt):
 @pytest.mark.parametrize("fmt,flag", [("Q4_0", 0), ("Q4_0", 0x100), ("Q4_1", 0), ("Q4_1", 0x100), ("Q8_0", 0)])
 @pytest.mark.parametrize("batch", [1, 3, 8, 13, 16, 27, 32])
 def test_workspace_entry_is_bit_identical(fmt, flag, batch):
-    """pfhe_quantized_gemv_ws repacks the activations first; same products, same order, same bits."""
+    """pfhe_quantized_gemv_ws repacks the activations first; same products, same order, same bits
+    (Q4_K, whose block sums then come from the repacking pass, is covered by test_q4_k_fused_gemv)."""
     rows, cols = 300, 1024
     t, raw, x = _case(fmt, rows, cols, batch, 7 * batch)
     t |= flag
@@ -78,7 +79,7 @@ def test_workspace_entry_is_bit_identical(fmt, flag, batch):
     _native.check(L.pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y0.data_ptr(),
                                         _native.OUT_F32, rows, st))
     nbytes = L.pfhe_quantized_gemv_workspace_bytes(cols, batch)
-    assert nbytes == cols // 32 * (1 if batch <= 8 else 2 if batch <= 16 else 4) * 512
+    assert nbytes == cols // 32 * (1 if batch <= 8 else 2 if batch <= 16 else 4) * (512 + 32)
     work = torch.empty(nbytes + 16, dtype=torch.uint8, device="cuda")
     _native.check(L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y1.data_ptr(),
                                            _native.OUT_F32, rows, work.data_ptr(), nbytes, st))
