@@ -20,6 +20,8 @@ Files written:
                      package (an independent implementation; the reference has no such mode)
   decode_<Q5_0|Q5_1|Q2_K..Q6_K>_ggml.npz  formats the reference cannot decode, decoded by gguf-py
   name_map.json      GGUFModel._map_tensor_name(...) of the reference for a list of tensor names
+  gguf_cuda_stream.npz  StreamingGGUFLoader.stream_tensor(...) and dequant_q4_0_cuda / dequant_q8_0_cuda of the
+                     reference's gguf_cuda.py on mini.gguf and on seeded blocks, run with device="cpu"
 """
 from __future__ import annotations
 
@@ -203,6 +205,26 @@ def main(ref_root: str) -> None:
             for k, dt in TORCH.items():
                 tens[f"{n}|{k}"] = bits(r.read_tensor(n, device="cpu", dtype=dt).reshape(-1))
             tens[f"{n}|raw"] = np.frombuffer(r.read_tensor_raw(n), dtype=np.uint8)
+    # --- the keep-quantised module's streaming loader and torch-op dequantisers, run on the CPU ------
+    # (gguf_cuda.py:52-246; with device="cpu" its tensor ops run on the host and give the bits its CUDA path gives)
+    from phfe.inference import gguf_cuda as ref_cuda
+    stream = {}
+    for k, dt in TORCH.items():
+        with ref_cuda.StreamingGGUFLoader(path, device="cpu", dtype=dt) as sl:
+            for n in sl.tensor_names:
+                try:
+                    stream[f"{n}|{k}"] = bits(sl.stream_tensor(n).reshape(-1))
+                except (ValueError, RuntimeError):          # Q4_1 (no decoder there) and element counts off a multiple of 32
+                    stream[f"{n}|{k}|unsupported"] = np.zeros(0, dtype=np.uint8)
+    rng = np.random.default_rng(99)
+    for fmt, fn, bb in ((Q4_0, ref_cuda.dequant_q4_0_cuda, 18), (Q8_0, ref_cuda.dequant_q8_0_cuda, 34)):
+        for numel in (32, 100, 4096 + 31):                      # the functions decode numel // 32 whole blocks
+            raw = synth.random_packed(fmt, -(-numel // 32) * 32, rng)
+            assert raw.size == -(-numel // 32) * bb
+            stream[f"fn|{NAMES[fmt]}|{numel}|raw"] = raw
+            stream[f"fn|{NAMES[fmt]}|{numel}|out"] = bits(fn(torch.from_numpy(raw.copy()), numel, "cpu"))
+    np.savez_compressed(os.path.join(HERE, "gguf_cuda_stream.npz"), **stream)
+
     # --- the caller's name map (model.py:377-420) ---------------------------------------------------
     from phfe.inference.model import GGUFModel
     probe = ["token_embd.weight", "output.weight", "output_norm.weight", "rope_freqs.weight", "blk.0.attn_q.weight",
