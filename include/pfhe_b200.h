@@ -211,7 +211,7 @@ int pfhe_device_status(int device);
 /*
  * Decode-time product on packed weights: y[m][n] = sum_k x[m][k] * W[n][k] for
  * batch m = 1..32, W of shape (rows, cols) kept in its GGUF block format (Q4_0,
- * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER, or Q4_K) and decoded
+ * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER, or Q4_K / Q5_K) and decoded
  * on the fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
  * (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight
  * to fp16 in device memory and then call F.linear.  Every Q4_0 / Q8_0 weight
@@ -220,7 +220,7 @@ int pfhe_device_status(int device);
  * fp32 first, one fp16 ulp apart in rare double-rounding cases).  x is fp16,
  * products and sums are fp32; the result differs from an fp32 reference on the
  * decoded weights by summation order (and, for Q4_1, by those rare ulps).
- * Q4_K multiplies with the unrounded fp32 weights (d*sc)*q - dmin*m of the
+ * Q4_K and Q5_K multiply with the unrounded fp32 weights (d*sc)*q - dmin*m of the
  * decode kernels' fp32 output (scales applied once per 32-element sub-block
  * after the tensor-core sum), i.e. without the fp16 rounding of each weight
  * that decode-to-fp16-then-multiply has.
@@ -239,7 +239,7 @@ int pfhe_quantized_gemv(int ggml_type, const void *w_dev, int64_t w_bytes, int64
  * batch) bytes, 16-byte aligned), so that each warp fetches its activations
  * with one coalesced load instead of a gather over up to eight rows of x and
  * four byte permutes.  Results are bit-identical to pfhe_quantized_gemv for
- * Q4_0, Q4_1 and Q8_0; for Q4_K the pass also sums each block's activations
+ * Q4_0, Q4_1 and Q8_0; for Q4_K / Q5_K the pass also sums each block's activations
  * (the kernel otherwise gets those sums from the tensor cores), so results
  * agree up to the fp32 order of that sum.  Worth
  * it from two rows of activations up, or for very large weights; with

@@ -82,7 +82,8 @@ template <int T> struct GemvFmt {
     static constexpr int kBase = T & ~T_ORDER_FLAG;
     static constexpr bool kGgml = (T & T_ORDER_FLAG) != 0;
     static constexpr bool kFour = kBase == T_Q4_0 || kBase == T_Q4_1;
-    static constexpr bool kSuper = kBase == T_Q4_K;          // 256-element super-block with 6-bit sub-block scales
+    static constexpr bool kSuper = kBase == T_Q4_K || kBase == T_Q5_K;   // 256-element super-blocks with 6-bit sub-block scales
+    static constexpr int kQsWord = kBase == T_Q5_K ? 12 : 4;  // first word of the nibble bytes (Q5_K: 32 bytes of fifth bits come first)
     static constexpr int kBB = Fmt<T>::kBytes * 32 / Fmt<T>::kElems;   // bytes per 32 elements (18 for Q4_K: 144 / 8)
     static constexpr int kPairWords = 2 * kBB / 4;          // 9, 10, 17 aligned words per pair of blocks
 };
@@ -186,9 +187,9 @@ template <int T> __device__ __forceinline__ void x_frags(const __half *xb, int t
     }
 }
 
-// ---- Q4_K: 144-byte super-blocks of 256 elements (fp16 d, fp16 dmin, 12 bytes of 6-bit scales and
-// minimums, 128 nibble bytes); y = (d * sc) * q - (dmin * m) per 32-element sub-block, as ggml's
-// dequantize_row_q4_K.  The kernel feeds the tensor cores 64 + q (exact in fp16, no subtract and
+// ---- Q4_K / Q5_K: 144- / 176-byte super-blocks of 256 elements (fp16 d, fp16 dmin, 12 bytes of 6-bit
+// scales and minimums, [Q5_K: 32 bytes of fifth bits,] 128 nibble bytes); y = (d * sc) * q - (dmin * m) per
+// 32-element sub-block, as ggml's dequantize_row_q4_K / _q5_K.  The kernel feeds the tensor cores 64 + q (exact in fp16, no subtract and
 // no per-weight multiply), gets sum_k x_k of the sub-block from a second instruction whose A
 // operand is all ones, and applies the two fp32 coefficients once per sub-block and output:
 //   acc += (d*sc) * sum((64 + q) x) - (64 * (d*sc) + dmin*m) * sum(x).
@@ -217,6 +218,13 @@ __device__ __forceinline__ void k4_coefficients(const K4Scales &s, int S, float 
     const float mn = byte_as_float(S < 4 ? s.m_lo : s.m_hi, S & 3);
     mul = __fmul_rn(s.d, sc);
     off = __fmaf_rn(64.0f, mul, __fmul_rn(s.dmin, mn));
+}
+// Q5_K: the fifth bit of sub-block S of the four elements of word v (bit S of each byte) added, as 16, to the
+// registers k4_nibbles made for those elements: mantissa bit 8 of each half.
+__device__ __forceinline__ void k5_high_bits(uint32_t v, int S, uint32_t (&r)[2])   // S is a constant after unrolling
+{
+    r[0] = and_or(v << (8 - S), 0x01000100u, r[0]);           // bytes 0 and 2
+    r[1] = and_or(v >> S, 0x01000100u, r[1]);                 // bytes 1 and 3
 }
 // From one word of four nibble bytes: lo[0..1] = 64 + low nibbles of bytes (0,2), (1,3);
 // hi[0..1] = 64 + high nibbles of the same bytes.
@@ -408,12 +416,19 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
         // Q4_K: the chunk is one super-block per row; sub-blocks 2J (low nibbles) and 2J+1 (high
         // nibbles) share the 32 bytes at qs + 32 J, of which this thread takes words t and t + 4.
         auto super_pair = [&](int J, const K4Scales &sa, const K4Scales &sb) {
-            const uint32_t *qa = rowA + 4 + 8 * J, *qb = rowB + 4 + 8 * J;
+            const uint32_t *qa = rowA + F::kQsWord + 8 * J, *qb = rowB + F::kQsWord + 8 * J;
             uint32_t al0[2], ah0[2], al1[2], ah1[2], bl0[2], bh0[2], bl1[2], bh1[2];
             k4_nibbles(qa[t], magic.hi, al0, ah0);
             k4_nibbles(qa[t + 4], magic.hi, al1, ah1);
             k4_nibbles(qb[t], magic.hi, bl0, bh0);
             k4_nibbles(qb[t + 4], magic.hi, bl1, bh1);
+            if constexpr (F::kBase == T_Q5_K) {                 // words 4..11: byte l holds the fifth bits of element l, bit S for sub-block S
+                const uint32_t va0 = rowA[4 + t], va1 = rowA[8 + t], vb0 = rowB[4 + t], vb1 = rowB[8 + t];
+                k5_high_bits(va0, 2 * J, al0); k5_high_bits(va0, 2 * J + 1, ah0);
+                k5_high_bits(va1, 2 * J, al1); k5_high_bits(va1, 2 * J + 1, ah1);
+                k5_high_bits(vb0, 2 * J, bl0); k5_high_bits(vb0, 2 * J + 1, bh0);
+                k5_high_bits(vb1, 2 * J, bl1); k5_high_bits(vb1, 2 * J + 1, bh1);
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 float mul_a, off_a, mul_b, off_b;
@@ -622,8 +637,8 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     int rc = type_geometry(ggml_type, &be, &bb);
     if (rc) return rc;
     const int base = ggml_type & ~T_ORDER_FLAG;
-    if (base != T_Q4_0 && base != T_Q4_1 && base != T_Q8_0 && ggml_type != T_Q4_K) {
-        set_error("pfhe_quantized_gemv handles Q4_0, Q4_1, Q8_0 and Q4_K weights, not ggml type %d", ggml_type);
+    if (base != T_Q4_0 && base != T_Q4_1 && base != T_Q8_0 && ggml_type != T_Q4_K && ggml_type != T_Q5_K) {
+        set_error("pfhe_quantized_gemv handles Q4_0, Q4_1, Q8_0, Q4_K and Q5_K weights, not ggml type %d", ggml_type);
         return PFHE_ERR_BAD_TYPE;
     }
     if (y_dtype != O_F32 && y_dtype != O_F16) { set_error("output dtype must be f32 or f16"); return PFHE_ERR_BAD_DTYPE; }
@@ -680,6 +695,7 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     case T_Q4_0G: return launch_gemv<T_Q4_0G>(a, stream);
     case T_Q4_1G: return launch_gemv<T_Q4_1G>(a, stream);
     case T_Q4_K: return launch_gemv<T_Q4_K>(a, stream);
+    case T_Q5_K: return launch_gemv<T_Q5_K>(a, stream);
     default: return launch_gemv<T_Q8_0>(a, stream);
     }
 }

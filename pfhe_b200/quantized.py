@@ -15,11 +15,11 @@ from typing import Optional, Tuple
 import torch
 
 from . import _native
-from .gguf_loader import (GGML_TYPE_F16, GGML_TYPE_F32, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q4_K, GGML_TYPE_Q8_0,
-                          QUANT_INFO)
+from .gguf_loader import (GGML_TYPE_F16, GGML_TYPE_F32, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q4_K, GGML_TYPE_Q5_K,
+                          GGML_TYPE_Q8_0, QUANT_INFO)
 from .resident import decode_resident
 
-GEMV_TYPES = (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K)
+GEMV_TYPES = (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_Q5_K)
 GEMV_MAX_BATCH = 32         # rows of activations the fused kernel takes in one launch
 # Repacking the activations into the kernel's consumption order costs one small launch (about 4 us)
 # and pays from roughly this many (packed weight bytes x activation rows) up; measured on B200.
@@ -75,7 +75,7 @@ def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int,
     """``x @ W.T`` for packed ``W`` of logical shape ``(out_features, in_features)``; returns fp16.
 
     ``x`` is ``[..., in_features]``.  At most 32 rows of activations, an in_features that is a multiple of
-    256 and a Q4_0 / Q4_1 / Q8_0 / Q4_K weight take the fused kernel; everything else decodes then multiplies.
+    256 and a Q4_0 / Q4_1 / Q8_0 / Q4_K / Q5_K weight take the fused kernel; everything else decodes then multiplies.
     """
     out_features, in_features = w_shape
     lead = x.shape[:-1]

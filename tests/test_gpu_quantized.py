@@ -68,7 +68,7 @@ def test_fused_gemv_many_rows(fmt):
 @pytest.mark.parametrize("batch", [1, 3, 8, 13, 16, 27, 32])
 def test_workspace_entry_is_bit_identical(fmt, flag, batch):
     """pfhe_quantized_gemv_ws repacks the activations first; same products, same order, same bits
-    (Q4_K, whose block sums then come from the repacking pass, is covered by test_q4_k_fused_gemv)."""
+    (Q4_K, whose block sums then come from the repacking pass, is covered by test_q4_k_q5_k_fused_gemv)."""
     rows, cols = 300, 1024
     t, raw, x = _case(fmt, rows, cols, batch, 7 * batch)
     t |= flag
@@ -98,11 +98,12 @@ def test_workspace_entry_is_bit_identical(fmt, flag, batch):
 @pytest.mark.parametrize("rows,cols", [(5, 512), (16, 256), (1000, 1024), (4096, 4096), (33, 8192)])
 @pytest.mark.parametrize("batch", [1, 3, 8, 13, 32])
 @pytest.mark.parametrize("workspace", [False, True])
-def test_q4_k_fused_gemv(rows, cols, batch, workspace):
+@pytest.mark.parametrize("t", [12, 13])
+def test_q4_k_q5_k_fused_gemv(t, rows, cols, batch, workspace):
     """Q4_K multiplies with the unrounded fp32 weights (d*sc)*q - dmin*m of ggml's decode, so the reference is the
     fp32 decode; the kernel forms (d*sc)*sum((64+q)x) - (64*d*sc + dmin*m)*sum(x) per sub-block, whose two terms
-    are up to ~20 times the size of their difference: tolerance 4e-5 of sum|w x| plus 2e-6 of max|w| * sum|x|."""
-    t = 12
+    are up to ~20 times the size of their difference: tolerance 4e-5 of sum|w x| plus 2e-6 of max|w| * sum|x|.
+    Q5_K (t = 13) is the same with a fifth bit per element."""
     raw = torch.from_numpy(synth.random_packed(t, rows * cols, np.random.default_rng(rows + batch))).cuda()
     g = torch.Generator(device="cuda").manual_seed(batch)
     x = torch.randn(batch, cols, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
