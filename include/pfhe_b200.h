@@ -211,7 +211,7 @@ int pfhe_device_status(int device);
 /*
  * Decode-time product on packed weights: y[m][n] = sum_k x[m][k] * W[n][k] for
  * batch m = 1..32, W of shape (rows, cols) kept in its GGUF block format (Q4_0,
- * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER, or Q4_K / Q5_K) and decoded
+ * Q4_1 or Q8_0, optionally with PFHE_TYPE_FLAG_GGML_ORDER, or Q4_K / Q5_K / Q6_K) and decoded
  * on the fly.  Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 of the reference
  * (src/phfe/inference/gguf_cuda.py:299-351), which dequantise the whole weight
  * to fp16 in device memory and then call F.linear.  Every Q4_0 / Q8_0 weight
@@ -223,8 +223,10 @@ int pfhe_device_status(int device);
  * Q4_K and Q5_K multiply with the unrounded fp32 weights (d*sc)*q - dmin*m of the
  * decode kernels' fp32 output (scales applied once per 32-element sub-block
  * after the tensor-core sum), i.e. without the fp16 rounding of each weight
- * that decode-to-fp16-then-multiply has.
- * cols must be a multiple of 256; w_dev and x_dev 16-byte
+ * that decode-to-fp16-then-multiply has; Q6_K likewise with (d*sc)*(q - 32),
+ * the scale applied to each 16-element sum.
+ * cols must be a multiple of 256 (2048 for Q6_K, whose rows must be whole
+ * 16-byte lines); w_dev and x_dev 16-byte
  * aligned; x is [batch][ldx] halves, y is [batch][ldy] of y_dtype (PFHE_OUT_F32
  * or PFHE_OUT_F16).
  */

@@ -78,14 +78,23 @@ __device__ __forceinline__ uint32_t h2_sub_fma(uint32_t x, uint32_t c, uint32_t 
     return *reinterpret_cast<uint32_t *>(&r);
 }
 
+__device__ __forceinline__ uint32_t h2_sub(uint32_t x, uint32_t c)         // exact for the small integers used here
+{
+    __half2 r = __hsub2_rn(*reinterpret_cast<__half2 *>(&x), *reinterpret_cast<__half2 *>(&c));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
 template <int T> struct GemvFmt {
     static constexpr int kBase = T & ~T_ORDER_FLAG;
     static constexpr bool kGgml = (T & T_ORDER_FLAG) != 0;
     static constexpr bool kFour = kBase == T_Q4_0 || kBase == T_Q4_1;
     static constexpr bool kSuper = kBase == T_Q4_K || kBase == T_Q5_K;   // 256-element super-blocks with 6-bit sub-block scales
     static constexpr int kQsWord = kBase == T_Q5_K ? 12 : 4;  // first word of the nibble bytes (Q5_K: 32 bytes of fifth bits come first)
-    static constexpr int kBB = Fmt<T>::kBytes * 32 / Fmt<T>::kElems;   // bytes per 32 elements (18 for Q4_K: 144 / 8)
-    static constexpr int kPairWords = 2 * kBB / 4;          // 9, 10, 17 aligned words per pair of blocks
+    static constexpr bool kSix = kBase == T_Q6_K;             // 210-byte super-blocks, int8 scales per 16 elements
+    static constexpr bool kByteOrder = kSuper || kSix;        // k slots follow bytes (0,2) (1,3) of a word, one byte per element
+    static constexpr int kChunkBytes = Fmt<T>::kBytes * 256 / Fmt<T>::kElems;   // a chunk is 256 elements: 144 .. 272 bytes
+    static constexpr int kBB = kChunkBytes / 8;               // bytes per 32 elements where that is whole (not Q6_K)
+    static constexpr int kPairWords = 2 * kBB / 4;            // 9, 10, 17 aligned words per pair of blocks
 };
 
 // Four half2 of weights from one 32-bit word of eight nibbles n0..n7 (n_i = bits 4i..4i+3):
@@ -168,7 +177,7 @@ template <int T> __device__ __forceinline__ void x_frags(const __half *xb, int t
     } else {
         const uint2 lo = __ldg(reinterpret_cast<const uint2 *>(xb + 4 * t));        // elements 4t .. 4t+3
         const uint2 hi = __ldg(reinterpret_cast<const uint2 *>(xb + 16 + 4 * t));   // elements 16+4t .. 16+4t+3
-        if constexpr (F::kSuper) {
+        if constexpr (F::kByteOrder) {
             // one byte per element, bytes 0 and 2 of a word extracted together: (4t, 4t+2) (4t+1, 4t+3), then 16 + the same
             b[0] = __byte_perm(lo.x, lo.y, 0x5410);
             b[1] = __byte_perm(lo.x, lo.y, 0x7632);
@@ -242,7 +251,7 @@ template <int T> __device__ __forceinline__ int slot_element(int t, int slot)
 {
     using F = GemvFmt<T>;
     const int reg = slot >> 1, hi = slot & 1;
-    if constexpr (F::kSuper) return 4 * t + 16 * (reg >> 1) + (reg & 1) + 2 * hi;          // (0,2) (1,3) (16,18) (17,19)
+    if constexpr (F::kByteOrder) return 4 * t + 16 * (reg >> 1) + (reg & 1) + 2 * hi;      // (0,2) (1,3) (16,18) (17,19)
     else if constexpr (F::kFour && !F::kGgml) return 8 * t + reg + 4 * hi;                 // (0,4) (1,5) (2,6) (3,7)
     else if constexpr (F::kFour) return 4 * t + 16 * (reg & 1) + (reg >> 1) + 2 * hi;      // (0,2) (16,18) (1,3) (17,19)
     else return 4 * t + 16 * (reg >> 1) + 2 * (reg & 1) + hi;                              // (0,1) (2,3) (16,17) (18,19)
@@ -312,10 +321,9 @@ inline int padded_pitch(int seg_bytes)
 // NT: batch tiles of eight activation rows (1, 2 or 4).  The decoded weights of a block pair are
 // used for every batch tile, so 32 rows cost about 1.9 times the instructions of 8, not 4 times.
 template <int T, int NT, bool kPacked>
-__global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper ? 4 : 5) : (NT == 2 ? 3 : 2)) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
+__global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kByteOrder ? 4 : 5) : (NT == 2 ? 3 : 2)) quant_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvArgs a)
 {
     using F = GemvFmt<T>;
-    constexpr int BB = F::kBB;
     constexpr int CB = kGemvChunkBlocks;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_all[kGemvWarps * kGemvStages];
@@ -346,7 +354,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
     const int n_mine = (n_chunks_total - ksplit + k_splits - 1) / k_splits;
 
     // One elected lane copies the 16 row segments of chunk c into stage s: a box of 16 rows by
-    // `pitch` bytes whose first coordinate (c * CB * BB bytes) is a multiple of 16 bytes.  The box
+    // `pitch` bytes whose first coordinate is the chunk's first byte rounded down to a multiple of 16
+    // (Q6_K chunks are 210 bytes, so all but every eighth start 2 .. 14 bytes into the box).  The box
     // is wider than the chunk by the padding; what it reads past the chunk is the next chunk's
     // first bytes or, past the end of a row or of the matrix, zero fill.  Neither is used.
     auto issue = [&](int i) {
@@ -357,7 +366,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
             asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                 ::"r"(smem_u32(ring + (size_t)s * stage_bytes)), "l"(reinterpret_cast<uint64_t>(&wmap)),
-                  "r"(c * (CB * BB / 4)), "r"((int)row0), "r"(smem_u32(&full[s])) : "memory");
+                  "r"(((c * F::kChunkBytes) & ~15) / 4), "r"((int)row0), "r"(smem_u32(&full[s])) : "memory");
         }
     };
     for (int i = 0; i < n_mine && i < kGemvStages; ++i) issue(i);
@@ -386,7 +395,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
         const uint32_t *rowA = reinterpret_cast<const uint32_t *>(ring + (size_t)s * stage_bytes + (size_t)g * pitch);
         const uint32_t *rowB = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(rowA) + 8 * pitch);
         auto pair = [&](int p) {                                // blocks 2p and 2p+1: a pair starts on a 4-byte boundary
-            if constexpr (F::kSuper) return;
+            if constexpr (F::kByteOrder) return;
             const uint32_t *WA = rowA + p * F::kPairWords;
             const uint32_t *WB = rowB + p * F::kPairWords;
             uint32_t ea[4], eb[4], oa[4], ob[4];
@@ -416,6 +425,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
         // Q4_K: the chunk is one super-block per row; sub-blocks 2J (low nibbles) and 2J+1 (high
         // nibbles) share the 32 bytes at qs + 32 J, of which this thread takes words t and t + 4.
         auto super_pair = [&](int J, const K4Scales &sa, const K4Scales &sb) {
+            if constexpr (!F::kSuper) return;
             const uint32_t *qa = rowA + F::kQsWord + 8 * J, *qb = rowB + F::kQsWord + 8 * J;
             uint32_t al0[2], ah0[2], al1[2], ah1[2], bl0[2], bh0[2], bl1[2], bh1[2];
             k4_nibbles(qa[t], magic.hi, al0, ah0);
@@ -464,7 +474,69 @@ __global__ void __launch_bounds__(kGemvWarps * 32, NT == 1 ? (GemvFmt<T>::kSuper
                 }
             }
         };
-        if constexpr (F::kSuper) {
+        // Q6_K: ql (128 nibble bytes), qh (64 bytes of bit pairs), 16 int8 scales, fp16 d; element 128 n + 32 q + l
+        // (q = 0..3, l = 0..31) has its low four bits in nibble q >> 1 of ql[64 n + 32 (q & 1) + l], its high two in
+        // bits 2q, 2q+1 of qh[32 n + l] and the scale 8 n + 2 q + l / 16, as ggml's dequantize_row_q6_K.  One
+        // tensor-core instruction covers one 16-element scale group; 1024 + q6 is formed in fp16, 1056 taken off
+        // exactly, and d * scale applied in fp32 to the sum.
+        auto six_chunk = [&]() {
+            const int skew = (c * F::kChunkBytes) & 15;         // where the super-block starts inside the copied box
+            const uint32_t sel = (skew & 2) ? 0x5432u : 0x3210u;
+            const uint32_t *WA = rowA + (skew >> 2), *WB = rowB + (skew >> 2);
+            auto word = [&](const uint32_t *W, int idx) { return __byte_perm(W[idx], W[idx + 1], sel); };   // bytes skew + 4 idx ..
+            const uint8_t *ba = reinterpret_cast<const uint8_t *>(rowA) + skew, *bb = reinterpret_cast<const uint8_t *>(rowB) + skew;
+            const float da = half_bits_to_f32(ld16<true>(ba + 208)), db = half_bits_to_f32(ld16<true>(bb + 208));
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                uint32_t qla[2][2], qlb[2][2], qha[2], qhb[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    qla[0][h] = word(WA, 16 * n + 4 * h + t);     qlb[0][h] = word(WB, 16 * n + 4 * h + t);
+                    qla[1][h] = word(WA, 16 * n + 8 + 4 * h + t); qlb[1][h] = word(WB, 16 * n + 8 + 4 * h + t);
+                    qha[h] = word(WA, 32 + 8 * n + 4 * h + t);    qhb[h] = word(WB, 32 + 8 * n + 4 * h + t);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t xs[NT][4];
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        if constexpr (kPacked) {
+                            const uint4 v = __ldg(a.xp + ((int64_t)(b0 + 4 * n + q) * NT + j) * 32 + lane);
+                            xs[j][0] = v.x; xs[j][1] = v.y; xs[j][2] = v.z; xs[j][3] = v.w;
+                        } else {
+                            x_frags<T>(xrow[j] + (int64_t)(b0 + 4 * n + q) * 32, t, xs[j]);
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        auto frag = [&](uint32_t w, uint32_t v, uint32_t &r0, uint32_t &r1) {
+                            const uint32_t lo = w >> (4 * (q >> 1));
+                            const uint32_t hi0 = q < 2 ? (v << (4 - 2 * q)) : (v >> (2 * q - 4));
+                            const uint32_t hi1 = v >> (2 * q + 4);
+                            r0 = h2_sub(and_or(lo, 0x000F000Fu, and_or(hi0, 0x00300030u, magic.lo)), 0x64206420u);       // bytes 0, 2
+                            r1 = h2_sub(and_or(lo >> 8, 0x000F000Fu, and_or(hi1, 0x00300030u, magic.lo)), 0x64206420u);  // bytes 1, 3
+                        };
+                        uint32_t a0, a1, c0, c1;
+                        frag(qla[q & 1][h], qha[h], a0, a1);
+                        frag(qlb[q & 1][h], qhb[h], c0, c1);
+                        const int si = 192 + 8 * n + 2 * q + h;
+                        const float sa = __fmul_rn(da, (float)(int)(int8_t)ba[si]), sb = __fmul_rn(db, (float)(int)(int8_t)bb[si]);
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            float dot[4] = {0.f, 0.f, 0.f, 0.f};
+                            mma_m16n8k16(dot, a0, c0, a1, c1, xs[j][2 * h], xs[j][2 * h + 1]);
+                            acc[j][0][0] = __fmaf_rn(sa, dot[0], acc[j][0][0]);
+                            acc[j][0][1] = __fmaf_rn(sa, dot[1], acc[j][0][1]);
+                            acc[j][0][2] = __fmaf_rn(sb, dot[2], acc[j][0][2]);
+                            acc[j][0][3] = __fmaf_rn(sb, dot[3], acc[j][0][3]);
+                        }
+                    }
+                }
+            }
+        };
+        if constexpr (F::kSix) {
+            six_chunk();
+        } else if constexpr (F::kSuper) {
             const K4Scales sa = k4_scales(rowA), sb = k4_scales(rowB);
 #pragma unroll
             for (int J = 0; J < 4; ++J) super_pair(J, sa, sb);
@@ -551,9 +623,9 @@ struct MapCache {
 };
 MapCache &map_cache() { static MapCache c; return c; }
 
-int make_weight_map(const GemvArgs &a, int block_bytes, CUtensorMap *map)
+int make_weight_map(const GemvArgs &a, int chunk_bytes, CUtensorMap *map)   // chunk_bytes: packed bytes of 256 elements
 {
-    const MapKey key{a.w, a.rows, a.k_blocks, block_bytes, a.pitch};
+    const MapKey key{a.w, a.rows, a.k_blocks, chunk_bytes, a.pitch};
     MapCache &c = map_cache();
     {
         std::lock_guard<std::mutex> lock(c.mu);
@@ -562,7 +634,7 @@ int make_weight_map(const GemvArgs &a, int block_bytes, CUtensorMap *map)
     }
     EncodeTiledFn enc = tensor_map_encoder();
     if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return PFHE_ERR_CUDA; }
-    const cuuint64_t row_bytes = (cuuint64_t)a.k_blocks * (cuuint64_t)block_bytes;
+    const cuuint64_t row_bytes = (cuuint64_t)(a.k_blocks / 8) * (cuuint64_t)chunk_bytes;
     const cuuint64_t gdim[2] = {row_bytes / 4, (cuuint64_t)a.rows};
     const cuuint64_t gstride[1] = {row_bytes};
     const cuuint32_t box[2] = {(cuuint32_t)(a.pitch / 4), 16u};
@@ -609,7 +681,7 @@ template <int T, int NT = 1, bool kPacked = false> int launch_gemv(const GemvArg
         configured.fetch_or(1ull << dev);
     }
     CUtensorMap wmap;
-    int rc = make_weight_map(a, GemvFmt<T>::kBB, &wmap);
+    int rc = make_weight_map(a, GemvFmt<T>::kChunkBytes, &wmap);
     if (rc) return rc;
     const int64_t grid = (a.rows + 16 * a.row_tiles - 1) / (16 * a.row_tiles);
     fn<<<(unsigned)grid, kGemvWarps * 32, smem, stream>>>(wmap, a);
@@ -637,8 +709,8 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     int rc = type_geometry(ggml_type, &be, &bb);
     if (rc) return rc;
     const int base = ggml_type & ~T_ORDER_FLAG;
-    if (base != T_Q4_0 && base != T_Q4_1 && base != T_Q8_0 && ggml_type != T_Q4_K && ggml_type != T_Q5_K) {
-        set_error("pfhe_quantized_gemv handles Q4_0, Q4_1, Q8_0, Q4_K and Q5_K weights, not ggml type %d", ggml_type);
+    if (base != T_Q4_0 && base != T_Q4_1 && base != T_Q8_0 && ggml_type != T_Q4_K && ggml_type != T_Q5_K && ggml_type != T_Q6_K) {
+        set_error("pfhe_quantized_gemv handles Q4_0, Q4_1, Q8_0, Q4_K, Q5_K and Q6_K weights, not ggml type %d", ggml_type);
         return PFHE_ERR_BAD_TYPE;
     }
     if (y_dtype != O_F32 && y_dtype != O_F16) { set_error("output dtype must be f32 or f16"); return PFHE_ERR_BAD_DTYPE; }
@@ -680,7 +752,12 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     a.batch = batch;
     a.ldx = ldx;
     a.ldy = ldy;
-    a.pitch = padded_pitch(kGemvChunkBlocks * (bb * 32 / be));
+    const int chunk_bytes = bb * 256 / be;                       // packed bytes of 256 elements
+    if ((cols / 256 * chunk_bytes) % 16) {
+        set_error("rows of %lld packed bytes are not a multiple of 16 (Q6_K needs cols to be a multiple of 2048)", (long long)(cols / 256 * chunk_bytes));
+        return PFHE_ERR_BAD_ARG;
+    }
+    a.pitch = padded_pitch(chunk_bytes + (chunk_bytes % 16 ? 14 : 0));
     // Two row tiles per CTA let pairs of warps share their activation reads through L1: measured
     // 3-13 % faster for the 4-bit formats from 128256 x 8192 up, slower for Q8_0 and for small matrices.
     a.row_tiles = (base != T_Q8_0 && rows >= 65536) ? 2 : 1;
@@ -696,6 +773,7 @@ extern "C" int pfhe_quantized_gemv_ws(int ggml_type, const void *w_dev, int64_t 
     case T_Q4_1G: return launch_gemv<T_Q4_1G>(a, stream);
     case T_Q4_K: return launch_gemv<T_Q4_K>(a, stream);
     case T_Q5_K: return launch_gemv<T_Q5_K>(a, stream);
+    case T_Q6_K: return launch_gemv<T_Q6_K>(a, stream);
     default: return launch_gemv<T_Q8_0>(a, stream);
     }
 }

@@ -16,10 +16,10 @@ import torch
 
 from . import _native
 from .gguf_loader import (GGML_TYPE_F16, GGML_TYPE_F32, GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q4_K, GGML_TYPE_Q5_K,
-                          GGML_TYPE_Q8_0, QUANT_INFO)
+                          GGML_TYPE_Q6_K, GGML_TYPE_Q8_0, QUANT_INFO)
 from .resident import decode_resident
 
-GEMV_TYPES = (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_Q5_K)
+GEMV_TYPES = (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_Q5_K, GGML_TYPE_Q6_K)
 GEMV_MAX_BATCH = 32         # rows of activations the fused kernel takes in one launch
 # Repacking the activations into the kernel's consumption order costs one small launch (about 4 us)
 # and pays from roughly this many (packed weight bytes x activation rows) up; measured on B200.
@@ -75,7 +75,7 @@ def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int,
     """``x @ W.T`` for packed ``W`` of logical shape ``(out_features, in_features)``; returns fp16.
 
     ``x`` is ``[..., in_features]``.  At most 32 rows of activations, an in_features that is a multiple of
-    256 and a Q4_0 / Q4_1 / Q8_0 / Q4_K / Q5_K weight take the fused kernel; everything else decodes then multiplies.
+    256 (2048 for Q6_K) and a Q4_0 / Q4_1 / Q8_0 / Q4_K / Q5_K / Q6_K weight take the fused kernel; everything else decodes then multiplies.
     """
     out_features, in_features = w_shape
     lead = x.shape[:-1]
@@ -84,7 +84,8 @@ def quantized_matmul(x: torch.Tensor, w_quant: torch.Tensor, w_shape: Tuple[int,
     ktype = quant_type
     if nibble_order == "ggml" and quant_type in (GGML_TYPE_Q4_0, GGML_TYPE_Q4_1):
         ktype |= _native.TYPE_FLAG_GGML_ORDER
-    fused = (quant_type in GEMV_TYPES and 1 <= batch <= GEMV_MAX_BATCH and in_features % 256 == 0
+    k_multiple = 2048 if quant_type == GGML_TYPE_Q6_K else 256      # Q6_K rows must be whole 16-byte lines (210-byte blocks)
+    fused = (quant_type in GEMV_TYPES and 1 <= batch <= GEMV_MAX_BATCH and in_features % k_multiple == 0
              and x2.is_cuda and w_quant.is_cuda and w_quant.data_ptr() % 16 == 0)
     if not fused:
         w = decode_resident([(w_quant.contiguous().view(torch.uint8), ktype, (out_features, in_features))], torch.float16)[0]

@@ -130,6 +130,47 @@ def test_q4_k_q5_k_fused_gemv(t, rows, cols, batch, workspace):
     assert bool(((y.double() - xd @ w16.T).abs() <= 2 ** -11 * bound + 4e-5 * bound + slack).all())
 
 
+@pytest.mark.parametrize("rows,cols", [(5, 2048), (16, 2048), (1000, 4096), (33, 8192), (4096, 14336)])
+@pytest.mark.parametrize("batch", [1, 5, 8, 13, 32])
+@pytest.mark.parametrize("workspace", [False, True])
+def test_q6_k_fused_gemv(rows, cols, batch, workspace):
+    """Q6_K multiplies with (d * sc) * (q6 - 32), the scale applied in fp32 to each 16-element sum; reference: the fp32
+    decode.  Super-blocks are 210 bytes, so seven of every eight start off the 16-byte lines the staging copies use."""
+    t = 14
+    raw = torch.from_numpy(synth.random_packed(t, rows * cols, np.random.default_rng(rows + batch))).cuda()
+    g = torch.Generator(device="cuda").manual_seed(batch)
+    x = torch.randn(batch, cols, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+    w32 = decode_resident([(raw, t, (rows, cols))], torch.float32)[0].double()
+    xd = x.double()
+    ref, bound = xd @ w32.T, xd.abs() @ w32.abs().T
+    L = _native.lib()
+    y = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    nws = L.pfhe_quantized_gemv_workspace_bytes(cols, batch)
+    work = torch.empty(nws, dtype=torch.uint8, device="cuda")
+    _native.check(L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y.data_ptr(),
+                                           _native.OUT_F32, rows, work.data_ptr() if workspace else None, nws,
+                                           torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    err = (y.double() - ref).abs()
+    assert bool((err <= 2e-5 * bound + 1e-30).all()), float((err / (2e-5 * bound + 1e-30)).max())
+    y16 = quantized_matmul(x, raw, (rows, cols), t)
+    assert y16.dtype == torch.float16
+    assert bool(((y16.double() - ref).abs() <= 2e-5 * bound + ref.abs() * 2 ** -10 + 1e-7).all())
+
+
+def test_q6_k_needs_rows_of_whole_lines():
+    L = _native.lib()
+    buf = torch.zeros(210 * 16 * 4, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(1, 1024, dtype=torch.float16, device="cuda")
+    y = torch.zeros(1, 16, dtype=torch.float32, device="cuda")
+    assert L.pfhe_quantized_gemv(14, buf.data_ptr(), buf.numel(), 16, 1024, x.data_ptr(), 1, 1024, y.data_ptr(), 0, 16, None) == _native.ERR_BAD_ARG
+    assert "2048" in _native.last_error()
+    t, raw, xx = 14, torch.from_numpy(synth.random_packed(14, 64 * 1024, np.random.default_rng(3))).cuda(), torch.randn(2, 1024, device="cuda").half()
+    w = decode_resident([(raw, t, (64, 1024))], torch.float16)[0]
+    assert torch.allclose(quantized_matmul(xx, raw, (64, 1024), t).float(), torch.nn.functional.linear(xx, w).float(), rtol=2e-3, atol=2e-3)
+
+
 def test_ggml_order_weights_and_wrappers():
     rows, cols = 512, 2048
     t, raw, x = _case("Q4_1", rows, cols, 2, 5)
@@ -193,7 +234,7 @@ def test_gemv_argument_errors():
     y = torch.zeros(8, 16, dtype=torch.float32, device="cuda")
     call = lambda t, rows, cols, batch, wbytes=4096, ydt=0: L.pfhe_quantized_gemv(t, buf.data_ptr(), wbytes, rows, cols, x.data_ptr(), batch,
                                                                                   256, y.data_ptr(), ydt, 16, None)
-    assert call(14, 16, 256, 1) == _native.ERR_BAD_TYPE                 # Q6_K has no fused kernel
+    assert call(11, 16, 256, 1) == _native.ERR_BAD_TYPE                 # Q3_K has no fused kernel
     assert call(2, 16, 128, 1) == _native.ERR_BAD_ARG                   # cols not a multiple of 256
     assert call(2, 16, 256, 33) == _native.ERR_BAD_ARG                  # batch > 32
     assert call(2, 16, 256, 1, wbytes=100) == _native.ERR_SHORT_SOURCE
