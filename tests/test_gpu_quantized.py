@@ -171,6 +171,24 @@ def test_q6_k_needs_rows_of_whole_lines():
     assert torch.allclose(quantized_matmul(xx, raw, (64, 1024), t).float(), torch.nn.functional.linear(xx, w).float(), rtol=2e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("t", [12, 13, 14])
+def test_k_quant_gemv_many_rows(t):
+    """The two-row-tile arrangement (65,536 rows and more) for the super-block formats, ragged last CTA included."""
+    rows, cols, batch = 65536 + 24, 2048, 3
+    raw = torch.from_numpy(synth.random_packed(t, rows * cols, np.random.default_rng(t))).cuda()
+    x = torch.randn(batch, cols, generator=torch.Generator(device="cuda").manual_seed(t), device="cuda").to(torch.float16)
+    w32 = decode_resident([(raw, t, (rows, cols))], torch.float32)[0]
+    xf = x.float()
+    ref, bound = (xf.double() @ w32.double().T), (xf.abs().double() @ w32.abs().double().T)
+    slack = 2e-6 * w32.abs().max().double() * xf.abs().double().sum(dim=1, keepdim=True)
+    y = torch.full((batch, rows), float("nan"), dtype=torch.float32, device="cuda")
+    _native.check(_native.lib().pfhe_quantized_gemv(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols,
+                                                   y.data_ptr(), _native.OUT_F32, rows, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _native.check(_native.lib().pfhe_device_status(-1))
+    assert bool(((y.double() - ref).abs() <= 4e-5 * bound + slack).all())
+
+
 def test_ggml_order_weights_and_wrappers():
     rows, cols = 512, 2048
     t, raw, x = _case("Q4_1", rows, cols, 2, 5)
