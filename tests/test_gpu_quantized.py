@@ -279,7 +279,7 @@ def test_packed_upload_and_linear_from_file(tmp_path):
                 assert bytes(packed.cpu().numpy().tobytes()) == r.read_tensor_raw(n)
             lin = load_quantized_linear(r, "a.weight")
             w = r.read_tensor("a.weight", device="cuda", dtype=torch.float16).float()
-            lin_k = load_quantized_linear(r, "b.weight")                      # a K-quant weight: decode-then-linear path
+            lin_k = load_quantized_linear(r, "b.weight")                      # a Q4_K weight: the fused kernel with fp32 sub-block scales
             wk = r.read_tensor("b.weight", device="cuda", dtype=torch.float16).float()
             with pytest.raises(ValueError):
                 load_quantized_linear(r, "n.weight")
