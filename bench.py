@@ -377,7 +377,7 @@ def run_gemv_leg(torch) -> dict:
     rows, cols = 28672, 8192
     st = torch.cuda.current_stream().cuda_stream
     out = {"weight": f"{rows}x{cols}", "unit": "GB/s of packed weight bytes", "timing": "40 launches over 4 rotated weights, CUDA events, best of 3"}
-    for name, t in (("Q4_0", 2), ("Q8_0", 8)):
+    for name, t in (("Q4_0", 2), ("Q8_0", 8), ("Q4_K", 12), ("Q6_K", 14)):
         nb = L.pfhe_tensor_nbytes(t, rows * cols)
         ws = [torch.randint(0, 255, (nb,), dtype=torch.uint8, device="cuda") for _ in range(4)]
         for batch in (1, 8):
