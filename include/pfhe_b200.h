@@ -22,14 +22,25 @@
 extern "C" {
 #endif
 
-/* ggml tensor type ids, as in gguf_loader.py:33-47 (only the six the reference decodes). */
+/*
+ * ggml tensor type ids, as in gguf_loader.py:33-47.  The first six are the ones the reference
+ * decodes; the rest are ids the reference names (:37-46) but cannot decode, decoded here in
+ * ggml's own element order and arithmetic (dequantize_row_q5_0 ... dequantize_row_q6_K).
+ */
 enum pfhe_ggml_type {
     PFHE_TYPE_F32 = 0,
     PFHE_TYPE_F16 = 1,
     PFHE_TYPE_Q4_0 = 2,
     PFHE_TYPE_Q4_1 = 3,
     PFHE_TYPE_Q8_0 = 8,
-    PFHE_TYPE_BF16 = 30
+    PFHE_TYPE_BF16 = 30,
+    PFHE_TYPE_Q5_0 = 6,
+    PFHE_TYPE_Q5_1 = 7,
+    PFHE_TYPE_Q2_K = 10,
+    PFHE_TYPE_Q3_K = 11,
+    PFHE_TYPE_Q4_K = 12,
+    PFHE_TYPE_Q5_K = 13,
+    PFHE_TYPE_Q6_K = 14
 };
 
 /*
@@ -47,9 +58,9 @@ enum pfhe_out_dtype { PFHE_OUT_F32 = 0, PFHE_OUT_F16 = 1, PFHE_OUT_BF16 = 2 };
 
 enum pfhe_status {
     PFHE_OK = 0,
-    PFHE_ERR_BAD_TYPE = -1,      /* ggml type outside the six above: NotImplementedError / ValueError in the reference (gguf_loader.py:134-135, :371-374) */
+    PFHE_ERR_BAD_TYPE = -1,      /* ggml type outside the list above: NotImplementedError / ValueError in the reference (gguf_loader.py:134-135, :371-374) */
     PFHE_ERR_BAD_DTYPE = -2,     /* output dtype not f32/f16/bf16 */
-    PFHE_ERR_SHORT_SOURCE = -3,  /* src_bytes < ceil(n/32)*block_bytes: ValueError "Data too short" (gguf_loader.py:444-446) */
+    PFHE_ERR_SHORT_SOURCE = -3,  /* src_bytes < ceil(n/block_elems)*block_bytes: ValueError "Data too short" (gguf_loader.py:444-446) */
     PFHE_ERR_SHORT_DEST = -4,    /* dst_bytes < n_elements * sizeof(out) */
     PFHE_ERR_BAD_ARG = -5,       /* NULL pointer, negative size, bad handle */
     PFHE_ERR_CUDA = -6,          /* a CUDA runtime call failed; see pfhe_last_error_string() */
