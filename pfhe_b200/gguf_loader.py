@@ -568,13 +568,19 @@ class StreamingDequantizer:
 
     def __init__(self, path: str | Path, batch_size: int = 4, device: str = "cuda",
                  dtype: torch.dtype = torch.float16, *, nibble_order: str = "reference",
-                 alignment: int | str = "reference"):
+                 alignment: int | str = "reference", prefetch: int = 0):
+        """prefetch: batches staged ahead of the one being consumed.  0 (the reference's behaviour) stages a batch
+        when the consumer asks for it; n > 0 stages the next n batches on a helper thread while the consumer works
+        on the current one, at the price of n more batches of decoded tensors alive at once."""
+        if prefetch < 0:
+            raise ValueError(f"prefetch must be >= 0, not {prefetch}")
         self.path = Path(path)
         self.batch_size = batch_size
         self.device = device
         self.dtype = dtype
         self.nibble_order = nibble_order
         self.alignment = alignment
+        self.prefetch = prefetch
         self._reader: Optional[GGUFReader] = None
 
     def open(self):
@@ -600,8 +606,42 @@ class StreamingDequantizer:
         the caller's; later batches never alias it."""
         reader = self._need_reader()
         names = self.tensor_names
-        for i in range(0, len(names), self.batch_size):
-            yield {n: reader.read_tensor(n, device=self.device, dtype=self.dtype) for n in names[i:i + self.batch_size]}
+        groups = [names[i:i + self.batch_size] for i in range(0, len(names), self.batch_size)]
+        if self.prefetch <= 0 or not groups:
+            for group in groups:
+                yield {n: reader.read_tensor(n, device=self.device, dtype=self.dtype) for n in group}
+            return
+
+        # Staging (host copy into the pinned ring) runs on a helper thread; the native call releases the GIL.
+        # The decodes are queued on the consumer's current stream, so work the consumer queues after receiving
+        # a batch is ordered behind that batch's decodes exactly as without prefetching.
+        from collections import deque
+        from concurrent.futures import ThreadPoolExecutor
+
+        _, cuda_dev = _cuda_device_for(self.device)
+        stream = torch.cuda.current_stream(cuda_dev)
+
+        def load(group):
+            with torch.cuda.device(cuda_dev), torch.cuda.stream(stream):
+                return {n: reader.read_tensor(n, device=self.device, dtype=self.dtype) for n in group}
+
+        with ThreadPoolExecutor(max_workers=1, thread_name_prefix="pfhe-prefetch") as pool:
+            pending = deque()
+            it = iter(groups)
+            for group in it:
+                pending.append(pool.submit(load, group))
+                if len(pending) > self.prefetch:
+                    break
+            try:
+                while pending:
+                    batch = pending.popleft().result()
+                    nxt = next(it, None)
+                    if nxt is not None:
+                        pending.append(pool.submit(load, nxt))
+                    yield batch
+            finally:
+                for f in pending:                       # the consumer stopped early: let queued loads finish or cancel
+                    f.cancel()
 
     def iter_tensors(self) -> Iterator[Tuple[str, torch.Tensor]]:
         reader = self._need_reader()
@@ -613,8 +653,9 @@ class StreamingDequantizer:
 def streaming_dequant_context(path: str | Path, batch_size: int = 4, device: str = "cuda",
                               dtype: torch.dtype = torch.float16, *,
                               nibble_order: str = "reference",
-                              alignment: int | str = "reference") -> Iterator[StreamingDequantizer]:
-    streamer = StreamingDequantizer(path, batch_size, device, dtype, nibble_order=nibble_order, alignment=alignment)
+                              alignment: int | str = "reference", prefetch: int = 0) -> Iterator[StreamingDequantizer]:
+    streamer = StreamingDequantizer(path, batch_size, device, dtype, nibble_order=nibble_order, alignment=alignment,
+                                    prefetch=prefetch)
     streamer.open()
     try:
         yield streamer

@@ -54,9 +54,10 @@ def _oracle_tensor(reader, name, dtype_key, via=None):
     return np_oracle.read_tensor(info.dtype, reader.read_tensor_raw(name), info.numel, dtype_key, via_dtype=via)
 
 
-def test_streaming_batches(small_llama):
+@pytest.mark.parametrize("prefetch", [0, 1, 3])
+def test_streaming_batches(small_llama, prefetch):
     path, _ = small_llama
-    with pfhe_b200.streaming_dequant_context(path, batch_size=8, device="cuda", dtype=torch.float16) as stream:
+    with pfhe_b200.streaming_dequant_context(path, batch_size=8, device="cuda", dtype=torch.float16, prefetch=prefetch) as stream:
         names = stream.tensor_names
         assert len(names) == 2 * 9 + 3
         seen, kept = [], []
@@ -71,6 +72,29 @@ def test_streaming_batches(small_llama):
                     assert t.is_cuda and t.dtype == torch.float16 and tuple(t.shape) == r.tensors[n].shape
                     assert_same_bits(to_bits(t), _oracle_tensor(r, n, "f16"), "f16", n)
         assert [n for n, _ in stream.iter_tensors()] == names
+
+
+def test_prefetched_batches_on_a_side_stream_and_early_exit(small_llama):
+    """Prefetching stages the next batches on a helper thread but queues their decodes on the consumer's stream:
+    work queued on that stream after a batch arrives sees the decoded values.  Leaving the loop early is clean."""
+    path, _ = small_llama
+    side = torch.cuda.Stream()
+    with gl.GGUFReader(path) as r:
+        want = {n: _oracle_tensor(r, n, "bf16") for n in r.tensors}
+    with torch.cuda.stream(side):
+        with pfhe_b200.streaming_dequant_context(path, batch_size=3, dtype=torch.bfloat16, prefetch=2) as stream:
+            copies = {}
+            for k, batch in enumerate(stream.iter_batches()):
+                for n, t in batch.items():
+                    copies[n] = t.clone()               # queued on `side`, behind the decode of t
+                if k == 2:
+                    break
+        side.synchronize()
+    assert len(copies) == 9
+    for n, t in copies.items():
+        assert_same_bits(to_bits(t), want[n], "bf16", n)
+    with pytest.raises(ValueError):
+        gl.StreamingDequantizer(path, prefetch=-1)
 
 
 def test_tensor_larger_than_a_staging_slot(tmp_path, monkeypatch):
