@@ -293,3 +293,36 @@ def test_packed_upload_and_linear_from_file(tmp_path):
     finally:
         gl._Stager.shutdown()
         gl._Stager.slot_bytes = old[0]
+
+
+# --- arbitrary shapes -------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+
+@settings(max_examples=80, deadline=None)
+@given(t=st.sampled_from([2, 3, 8, 12, 13, 14, 2 | 0x100, 3 | 0x100]), rows=st.integers(1, 200), kmul=st.integers(1, 6),
+       batch=st.integers(1, 32), workspace=st.booleans(), f16_out=st.booleans(), seed=st.integers(0, 2 ** 31 - 1))
+def test_fused_gemv_arbitrary_shapes(t, rows, kmul, batch, workspace, f16_out, seed):
+    """Any row count, any multiple of the column granule, any batch up to 32, both entry points and output types,
+    against the fp32 decode of the same bytes (the loosest of the per-format bars: 4e-5 of sum|w x| plus the
+    cancellation slack of the offset formats, plus one fp16 rounding when the output is fp16)."""
+    base = t & 0xFF
+    cols = (2048 if base == 14 else 256) * kmul
+    raw = torch.from_numpy(synth.random_packed(base, rows * cols, np.random.default_rng(seed))).cuda()
+    x = torch.randn(batch, cols, generator=torch.Generator(device="cuda").manual_seed(seed), device="cuda").to(torch.float16)
+    # Q4_0 / Q4_1 / Q8_0 multiply with the fp16-rounded weights, the K-quants with the fp32 ones
+    w = decode_resident([(raw, t, (rows, cols))], torch.float16 if base in (2, 3, 8) else torch.float32)[0].double()
+    xd = x.double()
+    ref, bound = xd @ w.T, xd.abs() @ w.abs().T
+    slack = 2e-6 * w.abs().max() * xd.abs().sum(dim=1, keepdim=True)
+    L = _native.lib()
+    y = torch.full((batch, rows), float("nan"), dtype=torch.float16 if f16_out else torch.float32, device="cuda")
+    nws = L.pfhe_quantized_gemv_workspace_bytes(cols, batch)
+    work = torch.empty(nws, dtype=torch.uint8, device="cuda")
+    _native.check(L.pfhe_quantized_gemv_ws(t, raw.data_ptr(), raw.numel(), rows, cols, x.data_ptr(), batch, cols, y.data_ptr(),
+                                           _native.OUT_F16 if f16_out else _native.OUT_F32, rows,
+                                           work.data_ptr() if workspace else None, nws, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _native.check(L.pfhe_device_status(-1))
+    tol = 4e-5 * bound + slack + (ref.abs() * 2 ** -10 + 1e-7 if f16_out else 0.0)
+    assert bool(((y.double() - ref).abs() <= tol).all())
